@@ -10,7 +10,8 @@ passed them; they are reused by later allocations.
 
 The reference has one cache shape for all layers (utils/engine.py:77-85, utils/kv_cache.py:84-89)
 and no per-request state in its paged path; groups and state slots are this engine's own.  Storage
-layout per group: [entry, k|v, page, kv_head, slot, head_dim].
+layout per group: [entry, k|v, page, kv_head, slot, head_dim]; where values have another size than keys, keys
+and values are two tensors of that layout without the k|v axis.
 """
 from __future__ import annotations
 
@@ -27,10 +28,16 @@ RELEASED = -1  # block-table entry of a page the window has passed
 @dataclass(frozen=True)
 class KVPagesNeed:
     """Keys and values of ``kv_heads`` heads of ``head_dim``; ``window`` None keeps all tokens,
-    else only the last ``window`` tokens are ever read."""
+    else only the last ``window`` tokens are ever read.  ``value_dim``: the size of a value head where it differs
+    from a key head's (None: the same)."""
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None
+
+    def __post_init__(self):
+        if self.value_dim is not None and int(self.value_dim) == int(self.head_dim):
+            object.__setattr__(self, "value_dim", None)     # one spelling per shape, so that equal needs share a group
 
 
 @dataclass(frozen=True)
@@ -49,7 +56,11 @@ class CacheGroup:
         self.pool = PagePool(num_pages)
         self.tables: Dict[object, List[int]] = {}
         self.released_upto: Dict[object, int] = {}   # per request: pages [0, n) were given back
-        self.storage = None               # torch tensor once materialised
+        # device tensors once materialised: ``key_storage`` [entry, page, kv_head, slot, head_dim] and ``value_storage``
+        # [entry, page, kv_head, slot, value_dim]; with equal sizes both are halves of ``storage`` [entry, k|v, ...]
+        self.storage = None
+        self.key_storage = None
+        self.value_storage = None
 
     @property
     def window(self) -> Optional[int]:
@@ -142,8 +153,13 @@ class CacheManager:
         self.device, self.dtype = device, dtype
         for group in self.groups:
             need = group.need
-            group.storage = torch.zeros((len(group.entries), 2, group.pool.num_pages, need.kv_heads, self.page_size,
-                                         need.head_dim), dtype=dtype, device=device)
+            shape = (len(group.entries), group.pool.num_pages, need.kv_heads, self.page_size)
+            if need.value_dim is None:
+                group.storage = torch.zeros((shape[0], 2) + shape[1:] + (need.head_dim,), dtype=dtype, device=device)
+                group.key_storage, group.value_storage = group.storage[:, 0], group.storage[:, 1]
+            else:
+                group.key_storage = torch.zeros(shape + (need.head_dim,), dtype=dtype, device=device)
+                group.value_storage = torch.zeros(shape + (int(need.value_dim),), dtype=dtype, device=device)
         for entry, need in self.state_entries.items():
             self.slots.storage[entry] = torch.zeros((self.slots.num_slots,) + tuple(need.shape),
                                                     dtype=getattr(torch, need.dtype), device=device)
@@ -151,8 +167,8 @@ class CacheManager:
     def pages_of_entry(self, entry: int):
         """(k_pages, v_pages, group index) of the schedule entry that owns a paged cache."""
         group_index, inside = self.group_of_entry[entry]
-        storage = self.groups[group_index].storage
-        return storage[inside, 0], storage[inside, 1], group_index
+        group = self.groups[group_index]
+        return group.key_storage[inside], group.value_storage[inside], group_index
 
     def state_of_entry(self, entry: int):
         return self.slots.storage[entry]
@@ -160,8 +176,9 @@ class CacheManager:
     def storage_bytes(self) -> int:
         total = 0
         for group in self.groups:
-            if group.storage is not None:
-                total += group.storage.numel() * group.storage.element_size()
+            for tensor in (group.key_storage, group.value_storage):
+                if tensor is not None:
+                    total += tensor.numel() * tensor.element_size()
         return total
 
     # ------------------------------------------------------------------ requests

@@ -33,8 +33,12 @@ def register_architecture(name: str, config_class: type, build_spec: Callable[[o
 
 def architecture_of(raw_config: dict) -> Architecture:
     names = raw_config.get("architectures") or []
+    if isinstance(names, str):
+        names = [names]
+    if not names and isinstance(raw_config.get("architecture"), str):
+        names = [raw_config["architecture"]]      # some configurations name their one architecture in the singular
     if not names:
-        raise UnsupportedModelError("config.json has no 'architectures' entry; cannot choose a model")
+        raise UnsupportedModelError("config.json has neither an 'architectures' nor an 'architecture' entry; cannot choose a model")
     if names[0] not in ARCHITECTURES:
         raise UnsupportedModelError(
             f"Architecture {names[0]!r} is not supported (supported: {', '.join(sorted(ARCHITECTURES))})")

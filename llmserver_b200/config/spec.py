@@ -63,9 +63,12 @@ class LayerSpec:
 @dataclass(frozen=True)
 class ScheduleEntry:
     """One execution of a layer.  ``cache_from`` names an earlier entry (by its index in the
-    schedule) whose cache this entry reads; None means the entry keeps a cache of its own."""
+    schedule) whose cache this entry reads; None means the entry keeps a cache of its own.
+    ``add_embedding``: the embedded tokens (the stream as it was before the first entry) are added
+    to the stream once more right before this entry runs."""
     layer: int
     cache_from: Optional[int] = None
+    add_embedding: bool = False
 
 
 @dataclass

@@ -12,6 +12,10 @@
 // Keys are visited 32 at a time from the first visible one, each lane owning one key's dot
 // product, so the order of every sum depends only on the query's position: the result for a token
 // is bit-identical however the prompt was cut into steps and whatever else is in the batch.
+//
+// Values may have another size than keys (`value_dim`; the output then has Hq * value_dim columns).  With `sinks`
+// (one 32-bit number per query head) the softmax's denominator also holds exp(sinks[h]): a score without a key
+// and without a value, not scaled, counted once.
 #include "common.cuh"
 
 #define ATTN_MAX_D 512
@@ -21,8 +25,9 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, int q_stride, 
                                          const T* __restrict__ v_pages, const int* __restrict__ block_tables,
                                          int max_blocks, const int* __restrict__ seq_of_token,
                                          const int* __restrict__ positions, T* __restrict__ out, int n_q_heads,
-                                         int n_kv_heads, int head_dim, int page_size, int num_pages, float scale,
-                                         int window, int* __restrict__ error_flag) {
+                                         int n_kv_heads, int head_dim, int value_dim, int page_size, int num_pages,
+                                         float scale, int window, const float* __restrict__ sinks,
+                                         int* __restrict__ error_flag) {
     pdl_trigger();   // let the next kernel start launching
     pdl_wait();      // everything before this kernel in the stream is complete and visible
     extern __shared__ float q_shared[];  // [warps][head_dim]
@@ -49,7 +54,7 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, int q_stride, 
     for (int base = first; base <= position; base += 32) {
         const int key = base + lane;
         const bool valid = key <= position;
-        long long offset = 0;  // element offset of this lane's key (and value) row inside the pages
+        long long offset = 0;  // this lane's key's slot in the pages: its key row lies at offset * head_dim, its value row at offset * value_dim
         float score = -INFINITY;
         if (valid) {
             int page = table[key / page_size];
@@ -57,8 +62,8 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, int q_stride, 
                 if (error_flag) atomicExch(error_flag, 5);
                 page = 0;
             }
-            offset = (((long long)page * n_kv_heads + kv_head) * page_size + key % page_size) * head_dim;
-            const T* k_row = k_pages + offset;
+            offset = ((long long)page * n_kv_heads + kv_head) * page_size + key % page_size;
+            const T* k_row = k_pages + offset * head_dim;
             float dot = 0.0f;
             for (int d = 0; d < head_dim; ++d) dot += q_row[d] * Num<T>::load(k_row + d);
             score = dot * scale;
@@ -74,32 +79,44 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, int q_stride, 
         for (int j = 0; j < in_chunk; ++j) {
             const float w = __shfl_sync(0xffffffffu, weight, j);
             const long long row = __shfl_sync(0xffffffffu, offset, j);
-            const T* v_row = v_pages + row;
+            const T* v_row = v_pages + row * value_dim;
 #pragma unroll
             for (int i = 0; i < ATTN_MAX_D / 32; ++i) {
                 const int d = lane + 32 * i;
-                if (d < head_dim) accumulator[i] += w * Num<T>::load(v_row + d);
+                if (d < value_dim) accumulator[i] += w * Num<T>::load(v_row + d);
             }
         }
         running_max = new_max;
     }
-    T* dst = out + (size_t)token * n_q_heads * head_dim + (size_t)head * head_dim;
+    if (sinks) {      // one more term of the denominator; it has no value, so the sums only shrink
+        const float sink = sinks[head];
+        const float new_max = fmaxf(running_max, sink);
+        const float correction = expf(running_max - new_max);
+        normaliser = normaliser * correction + expf(sink - new_max);
+#pragma unroll
+        for (int i = 0; i < ATTN_MAX_D / 32; ++i) accumulator[i] *= correction;
+    }
+    T* dst = out + (size_t)token * n_q_heads * value_dim + (size_t)head * value_dim;
     const float inverse = 1.0f / normaliser;
 #pragma unroll
     for (int i = 0; i < ATTN_MAX_D / 32; ++i) {
         const int d = lane + 32 * i;
-        if (d < head_dim) Num<T>::store(dst + d, accumulator[i] * inverse);
+        if (d < value_dim) Num<T>::store(dst + d, accumulator[i] * inverse);
     }
 }
 
 LLM_EXPORT int llm_attention_generic(const void* q, int q_stride, const void* k_pages, const void* v_pages,
                                      const int* block_tables, int max_blocks, const int* seq_of_token,
                                      const int* positions, void* out, int n_tokens, int n_q_heads, int n_kv_heads,
-                                     int head_dim, int page_size, int num_pages, float scale, int window,
-                                     int* error_flag, int dtype, cudaStream_t stream) {
+                                     int head_dim, int value_dim, int page_size, int num_pages, float scale, int window,
+                                     const float* sinks, int* error_flag, int dtype, cudaStream_t stream) {
     if (n_tokens == 0) return LLM_OK;
     if (head_dim > ATTN_MAX_D || head_dim <= 0) {
         llm_set_error("attention_generic: head_dim %d is outside 1..%d", head_dim, ATTN_MAX_D);
+        return LLM_REFUSED;
+    }
+    if (value_dim > ATTN_MAX_D || value_dim <= 0) {
+        llm_set_error("attention_generic: the value size %d is outside 1..%d", value_dim, ATTN_MAX_D);
         return LLM_REFUSED;
     }
     if (num_pages <= 0) {
@@ -116,6 +133,6 @@ LLM_EXPORT int llm_attention_generic(const void* q, int q_stride, const void* k_
     LLM_DISPATCH_DTYPE(dtype, (llm_launch(attention_generic_kernel<T>, grid, warps * 32, shared, stream, 
                                   (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_tables,
                                   max_blocks, seq_of_token, positions, (T*)out, n_q_heads, n_kv_heads, head_dim,
-                                  page_size, num_pages, scale, window, error_flag)));
+                                  value_dim, page_size, num_pages, scale, window, sinks, error_flag)));
     return llm_check_launch("attention_generic");
 }

@@ -157,3 +157,76 @@ LLM_EXPORT int llm_rmsnorm(const void* x, const void* weight, void* out, int n_r
                                   (const T*)x, (const W*)weight, (T*)out, width, eps)));
     return llm_check_launch("rmsnorm");
 }
+
+// A sub-layer whose output is normalised before it joins the stream, fused with the norm that follows:
+//   residual[r] += delta[r] * rsqrt(mean(delta[r]^2) + post_eps) * post_weight (+ extra[r])
+//   out[o]       = residual[r] * rsqrt(mean(residual[r]^2) + eps) * weight          (skipped when out is null)
+// `extra` is a second 32-bit stream added at the same time (a model that feeds its embedding in again).  Both
+// statistics, both products and the sum are 32-bit; the updated row waits in shared memory between the passes.
+template <typename T, typename W>
+__global__ void normed_add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                          const W* __restrict__ post_weight, float post_eps, const float* __restrict__ extra,
+                                          const W* __restrict__ weight, T* __restrict__ out, const int* __restrict__ rows,
+                                          int width, float eps, int write_residual) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[33];
+    extern __shared__ float updated[];     // [width]
+    const int o = blockIdx.x;
+    const int r = rows ? rows[o] : o;
+    float* res = residual + (size_t)r * width;
+    float inverse_post = 0.0f;
+    if (delta) {
+        const T* del = delta + (size_t)r * width;
+        float sum_squares = 0.0f;
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const float v = Num<T>::load(del + i);
+            updated[i] = v;
+            sum_squares += v * v;
+        }
+        inverse_post = rsqrtf(block_sum(sum_squares, scratch) / (float)width + post_eps);
+    }
+    float sum_squares = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = res[i];
+        if (delta) v += updated[i] * inverse_post * Num<W>::load(post_weight + i);
+        if (extra) v += extra[(size_t)r * width + i];
+        if (write_residual && (delta || extra)) res[i] = v;
+        updated[i] = v;
+        sum_squares += v * v;
+    }
+    if (!out) return;
+    const float inverse = rsqrtf(block_sum(sum_squares, scratch) / (float)width + eps);
+    T* dst = out + (size_t)o * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        Num<T>::store(dst + i, updated[i] * inverse * Num<W>::load(weight + i));
+}
+
+LLM_EXPORT int llm_normed_add_rmsnorm(float* residual, const void* delta, const void* post_weight, float post_eps,
+                                      const float* extra, const void* weight, void* out, const int* rows, int n_rows,
+                                      int width, float eps, int write_residual, int dtype, int weight_dtype,
+                                      cudaStream_t stream) {
+    if (n_rows == 0) return LLM_OK;
+    if (delta && !post_weight) {
+        llm_set_error("normed_add_rmsnorm: a delta needs the weight of its norm");
+        return LLM_REFUSED;
+    }
+    if (out && !weight) {
+        llm_set_error("normed_add_rmsnorm: an output needs the weight of its norm");
+        return LLM_REFUSED;
+    }
+    const size_t shared = (size_t)width * sizeof(float);
+    if (shared > 200 * 1024) {
+        llm_set_error("normed_add_rmsnorm: a width of %d needs %zu bytes of shared memory", width, shared);
+        return LLM_REFUSED;
+    }
+    LLM_DISPATCH_DTYPE_WEIGHT(dtype, weight_dtype, {
+        if (shared > 40 * 1024) {
+            const int status = llm_raise_shared_limit((const void*)normed_add_rmsnorm_kernel<T, W>, shared + 256, "normed_add_rmsnorm");
+            if (status != LLM_OK) return status;
+        }
+        llm_launch(normed_add_rmsnorm_kernel<T, W>, n_rows, norm_threads(width), shared, stream, residual, (const T*)delta,
+                   (const W*)post_weight, post_eps, extra, (const W*)weight, (T*)out, rows, width, eps, write_residual);
+    });
+    return llm_check_launch("normed_add_rmsnorm");
+}

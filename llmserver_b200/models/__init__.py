@@ -1,4 +1,4 @@
-from . import qwen3  # noqa: F401  (registers the architecture)
+from . import gefarax, qwen3  # noqa: F401  (register the architectures)
 from .decoder import DecoderModel
 from .loading import load_model, random_model
 

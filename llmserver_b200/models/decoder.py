@@ -15,6 +15,7 @@ from ..config.spec import ModelSpec
 from ..parts import BLOCKS, MIXERS, NORMS, POSITION_ENCODINGS, EntryCache, Runtime
 from ..parts.registry import parts_of_layer
 from ..parts.base import Block
+from ..parts.norm import NormedDelta
 
 
 class DecoderModel:
@@ -80,8 +81,20 @@ class DecoderModel:
             position.on_embedding(residual, batch)
         delta = None
         schedule = self.spec.schedule
+        embedded = None
+        if any(entry.add_embedding for entry in schedule):
+            # the stream is updated in place, so entries that take the embedded tokens in again read a second gather
+            embedded = ops.embedding(self.embedding, batch.token_ids)
+            for position in self.positions.values():
+                position.on_embedding(embedded, batch)
         for index, entry in enumerate(schedule):
             block = self.layers[entry.layer]
+            if entry.add_embedding:
+                if isinstance(delta, NormedDelta):
+                    delta.extra = embedded      # added by the kernel that adds the delta
+                else:
+                    ops.normed_add_rmsnorm(residual, None, None, 0.0, None, 0.0, extra=embedded, want_output=False,
+                                           act_dtype=self.runtime.dtype)
             if block.passes_stream:
                 # what runs next, for a block whose last part can prepare that norm's input
                 after = self.layers[schedule[index + 1].layer].entry() if index + 1 < len(schedule) else (self.final_norm, None)

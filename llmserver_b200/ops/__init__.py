@@ -16,7 +16,8 @@ from .library import (KernelError, call, check, declare, dtype_code, launch_coun
 from .stream import STREAM_ROWS, RowScaled, StreamSink
 
 __all__ = ["KernelError", "embedding", "add_rmsnorm", "rmsnorm", "silu_mul", "sample", "qk_norm_rope_kv_write",
-           "attention_generic", "gemm_f32", "linear", "qkv_projection", "gate_up_silu", "interleave_gate_up", "require_device", "library", "launch_count",
+           "attention_generic", "rope_kv_write_split", "normed_add_rmsnorm", "moe_route", "indexed_linear", "moe_combine",
+           "clamped_glu", "gemm_f32", "linear", "qkv_projection", "gate_up_silu", "interleave_gate_up", "require_device", "library", "launch_count",
            "RowScaled", "StreamSink", "STREAM_ROWS", "unscaled_rows_supported"]
 
 
@@ -190,26 +191,184 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k
 def attention_generic(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
                       block_tables: torch.Tensor, seq_of_token: torch.Tensor, positions: torch.Tensor,
                       n_q_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int = 0,
-                      out: Optional[torch.Tensor] = None, error_flag: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      out: Optional[torch.Tensor] = None, error_flag: Optional[torch.Tensor] = None,
+                      value_dim: Optional[int] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal (optionally windowed) attention of every token over its sequence's pages, 32-bit
-    arithmetic.  ``q`` holds head h of token n at q[n * q_stride + h * D]; returns [N, Hq * D].  A block-table entry
-    that names no page of the pool is not followed: page 0 is read instead and ``error_flag`` (default: the device's
-    shared flag) is set to 5."""
+    arithmetic.  ``q`` holds head h of token n at q[n * q_stride + h * D]; returns [N, Hq * Dv], Dv = ``value_dim``
+    (default D).  ``sinks`` (float32 [Hq]): one more term exp(sinks[h]) in each head's softmax denominator.  A
+    block-table entry that names no page of the pool is not followed: page 0 is read instead and ``error_flag``
+    (default: the device's shared flag) is set to 5."""
     check(q, "q")
     tokens = positions.numel()
+    value_dim = head_dim if value_dim is None else int(value_dim)
     check(k_pages, "k pages", q.dtype, head_dim)
-    check(v_pages, "v pages", q.dtype, head_dim)
+    check(v_pages, "v pages", q.dtype, value_dim)
+    if k_pages.shape[:-1] != v_pages.shape[:-1]:
+        raise KernelError(f"k pages {tuple(k_pages.shape)} and v pages {tuple(v_pages.shape)} differ in more than the last dimension")
     check(block_tables, "block_tables", torch.int32)
     check(seq_of_token, "seq_of_token", torch.int32)
     check(positions, "positions", torch.int32)
+    if sinks is not None:
+        check(sinks, "sinks", torch.float32)
+        if sinks.numel() != n_q_heads:
+            raise KernelError(f"sinks must hold one number per query head ({n_q_heads}), got {sinks.numel()}")
     if out is None:
-        out = torch.empty((tokens, n_q_heads * head_dim), dtype=q.dtype, device=q.device)
-    check(out, "attention output", q.dtype, n_q_heads * head_dim)
+        out = torch.empty((tokens, n_q_heads * value_dim), dtype=q.dtype, device=q.device)
+    check(out, "attention output", q.dtype, n_q_heads * value_dim)
     call("llm_attention_generic", q.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(),
          block_tables.data_ptr(), block_tables.shape[-1], seq_of_token.data_ptr(), positions.data_ptr(),
-         out.data_ptr(), tokens, n_q_heads, n_kv_heads, head_dim, k_pages.shape[2], k_pages.shape[0], float(scale),
-         int(window), (error_flag if error_flag is not None else wait_error_flag(q.device)).data_ptr(), dtype_code(q.dtype),
+         out.data_ptr(), tokens, n_q_heads, n_kv_heads, head_dim, value_dim, k_pages.shape[2], k_pages.shape[0],
+         float(scale), int(window), pointer(sinks),
+         (error_flag if error_flag is not None else wait_error_flag(q.device)).data_ptr(), dtype_code(q.dtype),
          stream_handle())
+    return out
+
+
+def rope_kv_write_split(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], magnitude: float, positions: torch.Tensor,
+                        seq_of_token: torch.Tensor, block_tables: torch.Tensor, k_pages: torch.Tensor,
+                        v_pages: torch.Tensor, n_q_heads: int, n_kv_heads: int, key_dim: int, value_dim: int,
+                        write_cache: bool, error_flag: torch.Tensor, rotary_dim: Optional[int] = None,
+                        interleaved: bool = False) -> None:
+    """In place on qkv [N, (Hq + Hkv) D + Hkv Dv]: the first ``rotary_dim`` elements of every Q and K head rotated by
+    position * inv_freq[i] with cos and sin multiplied by ``magnitude``; K heads written to the K pages
+    [page, Hkv, page_size, D], V heads copied to the V pages [page, Hkv, page_size, Dv]."""
+    if rotary_dim is None:
+        rotary_dim = 0 if inv_freq is None else 2 * inv_freq.numel()
+    check(qkv, "qkv", last_dim=(n_q_heads + n_kv_heads) * key_dim + n_kv_heads * value_dim)
+    tokens = qkv.shape[0]
+    if inv_freq is not None:
+        check(inv_freq, "inv_freq", torch.float32, rotary_dim // 2)
+    check(positions, "positions", torch.int32)
+    check(seq_of_token, "seq_of_token", torch.int32)
+    check(block_tables, "block_tables", torch.int32)
+    check(k_pages, "k pages", qkv.dtype, key_dim)
+    check(v_pages, "v pages", qkv.dtype, value_dim)
+    if k_pages.dim() != 4 or k_pages.shape[1] != n_kv_heads or k_pages.shape[:-1] != v_pages.shape[:-1]:
+        raise KernelError(f"pages must be [pages, {n_kv_heads}, page_size, {key_dim} | {value_dim}], got "
+                          f"{tuple(k_pages.shape)} and {tuple(v_pages.shape)}")
+    if positions.numel() != tokens or seq_of_token.numel() != tokens:
+        raise KernelError("positions and seq_of_token need one entry per token")
+    check(error_flag, "error flag", torch.int32)
+    call("llm_rope_kv_write_split", qkv.data_ptr(), pointer(inv_freq), float(magnitude), positions.data_ptr(),
+         seq_of_token.data_ptr(), block_tables.data_ptr(), block_tables.shape[-1], k_pages.data_ptr(), v_pages.data_ptr(),
+         tokens, n_q_heads, n_kv_heads, key_dim, value_dim, k_pages.shape[2], k_pages.shape[0], int(write_cache),
+         error_flag.data_ptr(), int(rotary_dim), int(bool(interleaved)), dtype_code(qkv.dtype), stream_handle())
+
+
+def normed_add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], post_weight: Optional[torch.Tensor],
+                       post_eps: float, weight: Optional[torch.Tensor], eps: float, extra: Optional[torch.Tensor] = None,
+                       rows: Optional[torch.Tensor] = None, act_dtype: Optional[torch.dtype] = None,
+                       want_output: bool = True) -> Optional[torch.Tensor]:
+    """residual += rmsnorm(delta) * post_weight (+ extra), all 32-bit and in place; then, unless ``want_output`` is
+    False, returns rmsnorm(residual) * weight in the activation type.  ``delta`` (activation type) and ``extra``
+    (float32, the stream's shape) may each be absent.  With ``rows`` (int32) output row o comes from row rows[o] and
+    the stream is left as it was."""
+    check(residual, "residual", torch.float32)
+    width = residual.shape[-1]
+    act = act_dtype or (delta.dtype if delta is not None else weight.dtype)
+    weight_dtype = None
+    for name, tensor in (("post-norm weight", post_weight), ("norm weight", weight)):
+        if tensor is not None:
+            check(tensor, name, last_dim=width)
+            if weight_dtype is not None and tensor.dtype != weight_dtype:
+                raise KernelError("the two norm weights must share a dtype")
+            weight_dtype = tensor.dtype
+    if delta is not None:
+        check(delta, "delta", act, width)
+        if delta.shape != residual.shape:
+            raise KernelError(f"delta {tuple(delta.shape)} does not match residual {tuple(residual.shape)}")
+    if extra is not None:
+        check(extra, "extra stream", torch.float32, width)
+        if extra.shape != residual.shape:
+            raise KernelError(f"extra {tuple(extra.shape)} does not match residual {tuple(residual.shape)}")
+    write_residual = rows is None
+    if rows is not None:
+        check(rows, "rows", torch.int32)
+        n_rows = rows.numel()
+    else:
+        n_rows = residual.numel() // width
+    out = torch.empty((n_rows, width), dtype=act, device=residual.device) if want_output else None
+    call("llm_normed_add_rmsnorm", residual.data_ptr(), pointer(delta), pointer(post_weight), float(post_eps), pointer(extra),
+         pointer(weight), pointer(out), pointer(rows), n_rows, width, float(eps), int(write_residual), dtype_code(act),
+         dtype_code(weight_dtype if weight_dtype is not None else act), stream_handle())
+    return out
+
+
+def moe_route(x: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], top: int, scale: float,
+              counts: Optional[torch.Tensor] = None):
+    """Per token the ``top`` experts with the largest sigmoid(router x) + correction (ties: the lower index) and their
+    weights sigmoid(router x) * scale: (chosen int32 [N, top], weights float32 [N, top]).  ``router`` [E, H] and
+    ``correction`` [E] are float32; with ``counts`` (int32 [E]) each choice also adds one to its expert's count."""
+    check(x, "x")
+    tokens, width = x.shape
+    check(router, "router weight", torch.float32, width)
+    experts = router.shape[0]
+    if correction is not None:
+        check(correction, "router correction", torch.float32, experts)
+    if counts is not None:
+        check(counts, "expert counts", torch.int32, experts)
+    chosen = torch.empty((tokens, top), dtype=torch.int32, device=x.device)
+    weights = torch.empty((tokens, top), dtype=torch.float32, device=x.device)
+    call("llm_moe_route", x.data_ptr(), router.data_ptr(), pointer(correction), chosen.data_ptr(), weights.data_ptr(),
+         pointer(counts), tokens, width, experts, int(top), float(scale), dtype_code(x.dtype), stream_handle())
+    return chosen, weights
+
+
+def indexed_linear(x: torch.Tensor, weight: torch.Tensor, index: Optional[torch.Tensor], pairs: int, in_div: int = 1,
+                   gated: Optional[tuple] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """out[p] = weight[index[p]] x[p // in_div] for p < ``pairs``; ``weight`` is [E, R, K] (``index`` None: E = 1).
+    ``gated`` = (limit, alpha): the matrices hold R gate rows and then R up rows, [E, 2 R, K], and the result is
+    min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + 1)."""
+    check(x, "x")
+    check(weight, "expert weights", x.dtype, x.shape[-1])
+    if weight.dim() != 3:
+        raise KernelError(f"expert weights must be [experts, rows, inner], got {tuple(weight.shape)}")
+    rows = weight.shape[1] // 2 if gated else weight.shape[1]
+    if index is not None:
+        check(index, "expert index", torch.int32)
+        if index.numel() < pairs:
+            raise KernelError(f"{index.numel()} expert indices for {pairs} pairs")
+    elif weight.shape[0] != 1:
+        raise KernelError("without an index the weights hold one matrix")
+    if x.shape[0] * in_div < pairs:
+        raise KernelError(f"{x.shape[0]} input rows cannot serve {pairs} pairs, {in_div} per row")
+    out_dtype = out_dtype or x.dtype
+    if out_dtype not in (x.dtype, torch.float32):
+        raise KernelError(f"indexed_linear writes the input's type or float32, not {out_dtype}")
+    out = torch.empty((pairs, rows), dtype=out_dtype, device=x.device)
+    limit, alpha = gated if gated else (0.0, 0.0)
+    call("llm_indexed_linear", x.data_ptr(), weight.data_ptr(), pointer(index), out.data_ptr(), pairs, rows, x.shape[-1],
+         int(in_div), int(bool(gated)), float(limit), float(alpha), dtype_code(x.dtype),
+         int(out_dtype == torch.float32 and x.dtype != torch.float32), stream_handle())
+    return out
+
+
+def moe_combine(down: torch.Tensor, weights: torch.Tensor, shared_out: Optional[torch.Tensor], act_dtype: torch.dtype) -> torch.Tensor:
+    """out[t] = sum_j weights[t, j] * down[t * top + j] (+ shared_out[t]); ``down`` float32 [N * top, H]."""
+    check(down, "expert outputs", torch.float32)
+    check(weights, "routing weights", torch.float32)
+    tokens, top = weights.shape
+    width = down.shape[-1]
+    if down.shape[0] != tokens * top:
+        raise KernelError(f"{down.shape[0]} expert outputs for {tokens} tokens with {top} experts each")
+    if shared_out is not None:
+        check(shared_out, "shared expert output", act_dtype, width)
+    out = torch.empty((tokens, width), dtype=act_dtype, device=down.device)
+    call("llm_moe_combine", down.data_ptr(), weights.data_ptr(), pointer(shared_out), out.data_ptr(), tokens, width, top,
+         dtype_code(act_dtype), stream_handle())
+    return out
+
+
+def clamped_glu(gate_up: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+    """out[n, i] = g * sigmoid(alpha * g) * (u + 1) with g = min(gate_up[n, i], limit) and u = gate_up[n, I + i] clamped
+    to [-limit, limit]; gate columns first."""
+    check(gate_up, "gate_up")
+    rows, doubled = gate_up.shape
+    if doubled % 2:
+        raise KernelError(f"gate_up's last dimension must be even, got {doubled}")
+    out = torch.empty((rows, doubled // 2), dtype=gate_up.dtype, device=gate_up.device)
+    call("llm_clamped_glu", gate_up.data_ptr(), out.data_ptr(), rows, doubled // 2, float(limit), float(alpha),
+         dtype_code(gate_up.dtype), stream_handle())
     return out
 
 
@@ -275,16 +434,19 @@ def qkv_projection(x, weight: torch.Tensor, q_weight: Optional[torch.Tensor], k_
 
 
 def attention(qkv: torch.Tensor, batch, block_tables: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
-              n_q_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> torch.Tensor:
+              n_q_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int = 0,
+              value_dim: Optional[int] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of a step's tokens over the paged cache; ``qkv`` is the packed projection whose Q
     heads have been normalised and rotated in place.  Chooses the kernel by dtype, head size and the
-    shape of the batch; every choice computes the same function."""
-    q_stride = (n_q_heads + 2 * n_kv_heads) * head_dim
-    if qkv.dtype == torch.bfloat16:
+    shape of the batch; every choice computes the same function.  ``value_dim`` (default: head_dim) and ``sinks`` as
+    in ``attention_generic``."""
+    value_dim = head_dim if value_dim is None else int(value_dim)
+    q_stride = (n_q_heads + n_kv_heads) * head_dim + n_kv_heads * value_dim
+    if qkv.dtype == torch.bfloat16 and value_dim == head_dim and sinks is None:
         from . import attention_bf16
         result = attention_bf16.try_attention(qkv, q_stride, batch, block_tables, k_pages, v_pages, n_q_heads,
                                               n_kv_heads, head_dim, scale, window)
         if result is not None:
             return result
     return attention_generic(qkv, q_stride, k_pages, v_pages, block_tables, batch.seq_of_token, batch.positions,
-                             n_q_heads, n_kv_heads, head_dim, scale, window)
+                             n_q_heads, n_kv_heads, head_dim, scale, window, value_dim=value_dim, sinks=sinks)

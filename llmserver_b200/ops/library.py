@@ -23,7 +23,13 @@ SIGNATURES = {
     "llm_sample": [_P, _P, _P, _P, _P, _I, _I, _P, _P, _S],
     "llm_sample_slices": [_I, _I],
     "llm_qk_norm_rope_kv_write": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _I, _I, _I, _S],
-    "llm_attention_generic": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _S],
+    "llm_attention_generic": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _I, _S],
+    "llm_rope_kv_write_split": [_P, _P, _F, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _I, _S],
+    "llm_normed_add_rmsnorm": [_P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I, _S],
+    "llm_moe_route": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _S],
+    "llm_indexed_linear": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _S],
+    "llm_moe_combine": [_P, _P, _P, _P, _I, _I, _I, _I, _S],
+    "llm_clamped_glu": [_P, _P, _I, _I, _F, _F, _I, _S],
     "llm_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _S],
     "llm_attention_mma_supports": [_I, _I, _I],
     "llm_attention_prefill_tcgen05_supports": [_I, _I, _I, _I],

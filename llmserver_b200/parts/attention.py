@@ -8,7 +8,7 @@ import torch
 
 from .. import ops
 from ..cache.manager import KVPagesNeed
-from ..weights.declare import NORM, WeightDecl
+from ..weights.declare import NORM, WIDE, WeightDecl
 from .base import Mixer
 from .registry import MIXERS
 
@@ -24,14 +24,30 @@ class GQAttention(Mixer):
     Parameters: ``hidden``, ``heads``, ``kv_heads``, ``head_dim``, ``scale``, ``qk_norm`` (bool),
     ``eps`` (of the Q/K norms), ``window`` (None = all keys; else a query at position p reads keys
     p - window + 1 .. p).  ``bias`` and ``softcap`` are known and must be off: the kernels have neither a bias
-    epilogue nor score capping, and say so instead of computing without them.
+    epilogue nor score capping, and say so instead of computing without them.  ``value_dim``: the size of a value
+    head where it differs from ``head_dim`` (the output projection then reads heads * value_dim columns).  ``sinks``
+    (bool): a learned number per query head joins each softmax's denominator as exp(sink), without a key or a value,
+    neither scaled nor masked.  ``names``: pairs (role, tensor name behind the prefix) for checkpoints that call the
+    tensors otherwise; roles are q, k, v, o, q_norm, k_norm, sinks.
 
     How positions are encoded comes from the position encoding the layer names (``attach``): its inverse
     frequencies, how many elements of a head rotate (``rotary_dim``, at most head_dim) and how they pair
     ("halves" or "interleaved").  An encoding that scales the rotated values (``attention_factor`` other than 1) is
-    refused: the rotation kernel does not scale."""
+    goes through the rotation kernel that takes a magnitude, which has no per-head norm: with ``qk_norm`` it is
+    refused.  The same kernel serves heads whose values have another size than their keys."""
 
-    KNOWN_PARAMS = ("hidden", "heads", "kv_heads", "head_dim", "scale", "qk_norm", "eps", "window", "bias", "softcap")
+    KNOWN_PARAMS = ("hidden", "heads", "kv_heads", "head_dim", "scale", "qk_norm", "eps", "window", "bias", "softcap",
+                    "value_dim", "sinks", "names")
+    NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+             "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "sinks": "sinks"}
+
+    @classmethod
+    def names(cls, params) -> dict:
+        given = dict(params.get("names") or ())
+        unknown = sorted(set(given) - set(cls.NAMES))
+        if unknown:
+            raise ValueError(f"gqa_attention has no tensor in the role(s) {', '.join(unknown)}")
+        return {**cls.NAMES, **given}
 
     @classmethod
     def check_params(cls, params):
@@ -44,18 +60,23 @@ class GQAttention(Mixer):
     @classmethod
     def declare_weights(cls, params):
         hidden, heads, kv_heads, dim = params["hidden"], params["heads"], params["kv_heads"], params["head_dim"]
-        wanted = {"q_proj.weight": WeightDecl((heads * dim, hidden)),
-                  "k_proj.weight": WeightDecl((kv_heads * dim, hidden)),
-                  "v_proj.weight": WeightDecl((kv_heads * dim, hidden)),
-                  "o_proj.weight": WeightDecl((hidden, heads * dim))}
+        value_dim = params.get("value_dim") or dim
+        name = cls.names(params)
+        wanted = {name["q"]: WeightDecl((heads * dim, hidden)),
+                  name["k"]: WeightDecl((kv_heads * dim, hidden)),
+                  name["v"]: WeightDecl((kv_heads * value_dim, hidden)),
+                  name["o"]: WeightDecl((hidden, heads * value_dim))}
         if params.get("qk_norm"):
-            wanted["q_norm.weight"] = WeightDecl((dim,), NORM)
-            wanted["k_norm.weight"] = WeightDecl((dim,), NORM)
+            wanted[name["q_norm"]] = WeightDecl((dim,), NORM)
+            wanted[name["k_norm"]] = WeightDecl((dim,), NORM)
+        if params.get("sinks"):
+            wanted[name["sinks"]] = WeightDecl((heads,), WIDE)
         return wanted
 
     @classmethod
     def cache_need(cls, params):
-        return KVPagesNeed(int(params["kv_heads"]), int(params["head_dim"]), params.get("window"))
+        return KVPagesNeed(int(params["kv_heads"]), int(params["head_dim"]), params.get("window"),
+                           int(params["value_dim"]) if params.get("value_dim") else None)
 
     def __init__(self, params, weights, runtime):
         super().__init__(params, weights, runtime)
@@ -65,11 +86,18 @@ class GQAttention(Mixer):
         self.scale = float(params["scale"])
         self.window = int(params["window"]) if params.get("window") else 0
         self.eps = float(params.get("eps", 0.0))
-        self.qkv = torch.cat([weights["q_proj.weight"], weights["k_proj.weight"], weights["v_proj.weight"]], dim=0).contiguous()
-        self.out = weights["o_proj.weight"].contiguous()
-        self.q_norm = weights["q_norm.weight"].contiguous() if params.get("qk_norm") else None
-        self.k_norm = weights["k_norm.weight"].contiguous() if params.get("qk_norm") else None
-        self.inv_freq, self.rotary_dim, self.interleaved = None, self.head_dim, False
+        self.value_dim = int(params.get("value_dim") or self.head_dim)
+        name = self.names(params)
+        self.qkv = torch.cat([weights[name["q"]], weights[name["k"]], weights[name["v"]]], dim=0).contiguous()
+        self.out = weights[name["o"]].contiguous()
+        self.q_norm = weights[name["q_norm"]].contiguous() if params.get("qk_norm") else None
+        self.k_norm = weights[name["k_norm"]].contiguous() if params.get("qk_norm") else None
+        self.sinks = weights[name["sinks"]].to(torch.float32).contiguous() if params.get("sinks") else None
+        self.inv_freq, self.rotary_dim, self.interleaved, self.magnitude = None, self.head_dim, False, 1.0
+        # keys and values of different sizes are rotated and cached by the kernel for split sizes
+        self.split = self.value_dim != self.head_dim
+        if self.split and params.get("qk_norm"):
+            raise ValueError("gqa_attention: per-head Q/K norms with values of another size than the keys are not supported")
 
     def attach(self, position):
         """``position``: None (no rotation) or an encoding with ``inv_freq`` (float32 [rotary_dim / 2] on the device)
@@ -87,22 +115,32 @@ class GQAttention(Mixer):
         pairing = getattr(position, "pairing", "halves")
         if pairing not in ("halves", "interleaved"):
             raise ValueError(f"gqa_attention pairs rotated elements as 'halves' or 'interleaved', not {pairing!r}")
-        if float(getattr(position, "attention_factor", 1.0)) != 1.0:
-            raise ValueError("gqa_attention's rotation kernel does not scale the rotated values: the position encoding's "
-                             f"attention_factor is {position.attention_factor}, only 1 is supported")
+        self.magnitude = float(getattr(position, "attention_factor", 1.0))
+        if self.magnitude != 1.0:
+            if self.q_norm is not None:
+                raise ValueError("gqa_attention: the rotation kernel that applies per-head Q/K norms does not scale the rotated "
+                                 f"values, and the position encoding's attention_factor is {self.magnitude}")
+            self.split = True
         self.inv_freq, self.rotary_dim, self.interleaved = inv_freq, rotary_dim, pairing == "interleaved"
 
     feeds_stream = True
 
     @functools.cached_property
     def takes_unscaled(self):
-        return ops.unscaled_rows_supported(self.qkv)
+        return not self.split and ops.unscaled_rows_supported(self.qkv)
 
     def forward(self, x, batch, cache, sink=None):
         tables = batch.block_tables[cache.group]
-        qkv = ops.qkv_projection(x, self.qkv, self.q_norm, self.k_norm, self.inv_freq, batch.positions, batch.seq_of_token,
-                                 tables, cache.k_pages, cache.v_pages, self.heads, self.kv_heads, self.head_dim, self.eps,
-                                 cache.writes, batch.error_flag, self.rotary_dim, self.interleaved)
+        if self.split:
+            qkv = ops.linear(x, self.qkv)
+            ops.rope_kv_write_split(qkv, self.inv_freq, self.magnitude, batch.positions, batch.seq_of_token, tables,
+                                    cache.k_pages, cache.v_pages, self.heads, self.kv_heads, self.head_dim, self.value_dim,
+                                    cache.writes, batch.error_flag, self.rotary_dim if self.inv_freq is not None else 0,
+                                    self.interleaved)
+        else:
+            qkv = ops.qkv_projection(x, self.qkv, self.q_norm, self.k_norm, self.inv_freq, batch.positions, batch.seq_of_token,
+                                     tables, cache.k_pages, cache.v_pages, self.heads, self.kv_heads, self.head_dim, self.eps,
+                                     cache.writes, batch.error_flag, self.rotary_dim, self.interleaved)
         attended = ops.attention(qkv, batch, tables, cache.k_pages, cache.v_pages, self.heads, self.kv_heads,
-                                 self.head_dim, self.scale, self.window)
+                                 self.head_dim, self.scale, self.window, value_dim=self.value_dim, sinks=self.sinks)
         return ops.linear(attended, self.out, sink=sink)

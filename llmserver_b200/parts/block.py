@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 from .base import Block
+from .norm import NormedDelta
 from .registry import BLOCKS
 
 
@@ -38,3 +39,33 @@ def _add_norm(norm, residual, delta, consumer):
     if getattr(consumer, "takes_unscaled", False) and norm.sink(residual, consumer) is not None:
         return norm.add_norm(residual, delta, unscaled=True)
     return norm.add_norm(residual, delta)
+
+
+@BLOCKS.register("sandwich_norm")
+class SandwichNormBlock(Block):
+    """A norm in front of and behind each sub-layer:
+
+        h += mixer_out_norm(mixer(mixer_norm(h)));  h += feed_forward_out_norm(feed_forward(feed_forward_norm(h)))
+
+    A sub-layer's output is not added by itself: it travels on as a ``NormedDelta`` and the next norm's kernel
+    normalises it, adds it to the 32-bit stream and normalises the stream in one pass (the model's final norm does the
+    same for the last layer).  Parameters: ``feed_forward`` (default True; False: the layer is its mixer alone) and
+    the tensor-name prefixes of its parts (``mixer_prefix``, ``mixer_norm_prefix``, ``mixer_out_norm_prefix`` ...)."""
+
+    KNOWN_PARAMS = ("feed_forward", "mixer_prefix", "feed_forward_prefix", "mixer_norm_prefix", "mixer_out_norm_prefix",
+                    "feed_forward_norm_prefix", "feed_forward_out_norm_prefix")
+
+    @classmethod
+    def roles(cls, params):
+        roles = {"mixer": "mixer", "mixer_norm": "norm", "mixer_out_norm": "norm"}
+        if params.get("feed_forward", True):
+            roles.update({"feed_forward": "feed_forward", "feed_forward_norm": "norm", "feed_forward_out_norm": "norm"})
+        return roles
+
+    def forward(self, residual, delta, batch, cache):
+        mixed = self.mixer.forward(self.mixer_norm.add_norm(residual, delta), batch, cache)
+        pending = NormedDelta(mixed, self.mixer_out_norm)
+        if not self.params.get("feed_forward", True):
+            return residual, pending
+        out = self.feed_forward.forward(self.feed_forward_norm.add_norm(residual, pending))
+        return residual, NormedDelta(out, self.feed_forward_out_norm)

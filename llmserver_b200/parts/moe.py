@@ -1,0 +1,85 @@
+"""A routed feed-forward: many small gated experts of which each token uses a few, and an optional shared one."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..weights.declare import WIDE, WeightDecl
+from .base import FeedForward
+from .registry import FEED_FORWARDS
+
+
+@FEED_FORWARDS.register("routed_experts")
+class RoutedExperts(FeedForward):
+    """y = sum over the chosen experts e of w_e * expert_e(x)  (+ shared(x)).
+
+    Router: z = W_r x in 32-bit, s = sigmoid(z).  The ``top`` experts with the largest s + correction are chosen (the
+    correction, a learned number per expert, only steers the choice; ties go to the lower index); their weights are
+    s * ``route_scale``, not renormalised.  An expert is a gated feed-forward without biases:
+
+        g = min(W_gate x, limit),  u = clamp(W_up x, -limit, limit),  expert(x) = W_down (g * sigmoid(alpha * g) * (u + 1))
+
+    and the shared expert, which every token uses with weight 1, has the same form with sizes and a limit of its own.
+
+    Parameters: ``hidden``, ``experts``, ``top``, ``intermediate``, ``limit``, ``route_scale``; ``alpha`` (default
+    1.702); ``correction`` (default True: the router has one); ``shared_intermediate`` and ``shared_limit`` (absent: no
+    shared expert).  Tensors behind the part's prefix: ``e<i>.gate``, ``e<i>.up`` [intermediate, hidden], ``e<i>.down``
+    [hidden, intermediate], ``router`` [experts, hidden], ``correction`` [experts], ``shared.gate`` / ``.up`` /
+    ``.down``.  Router and correction are held in float32 in either path."""
+
+    KNOWN_PARAMS = ("hidden", "experts", "top", "intermediate", "limit", "route_scale", "alpha", "correction",
+                    "shared_intermediate", "shared_limit")
+
+    @classmethod
+    def check_params(cls, params):
+        super().check_params(params)
+        if not 0 < int(params["top"]) <= int(params["experts"]):
+            raise ValueError(f"routed_experts: top {params['top']} must lie in 1..experts ({params['experts']})")
+
+    @classmethod
+    def declare_weights(cls, params):
+        hidden, inter = int(params["hidden"]), int(params["intermediate"])
+        wanted = {}
+        for e in range(int(params["experts"])):
+            wanted[f"e{e}.gate"] = WeightDecl((inter, hidden))
+            wanted[f"e{e}.up"] = WeightDecl((inter, hidden))
+            wanted[f"e{e}.down"] = WeightDecl((hidden, inter))
+        wanted["router"] = WeightDecl((int(params["experts"]), hidden), WIDE)
+        if params.get("correction", True):
+            wanted["correction"] = WeightDecl((int(params["experts"]),), WIDE)
+        if params.get("shared_intermediate"):
+            shared = int(params["shared_intermediate"])
+            wanted["shared.gate"] = WeightDecl((shared, hidden))
+            wanted["shared.up"] = WeightDecl((shared, hidden))
+            wanted["shared.down"] = WeightDecl((hidden, shared))
+        return wanted
+
+    def __init__(self, params, weights, runtime):
+        super().__init__(params, weights, runtime)
+        self.experts, self.top = int(params["experts"]), int(params["top"])
+        self.limit, self.alpha = float(params["limit"]), float(params.get("alpha", 1.702))
+        self.route_scale = float(params["route_scale"])
+        # one tensor per kind of matrix: [E, 2 I, H] with an expert's gate rows in front of its up rows, and [E, H, I]
+        self.gate_up = torch.stack([torch.cat([weights[f"e{e}.gate"], weights[f"e{e}.up"]], dim=0)
+                                    for e in range(self.experts)]).contiguous()
+        self.down = torch.stack([weights[f"e{e}.down"] for e in range(self.experts)]).contiguous()
+        self.router = weights["router"].to(torch.float32).contiguous()
+        self.correction = weights["correction"].to(torch.float32).contiguous() if params.get("correction", True) else None
+        self.shared_gate_up = self.shared_down = None
+        if params.get("shared_intermediate"):
+            self.shared_gate_up = torch.cat([weights["shared.gate"], weights["shared.up"]], dim=0).contiguous()
+            self.shared_down = weights["shared.down"].contiguous()
+            self.shared_limit = float(params.get("shared_limit", self.limit))
+
+    def forward(self, x):
+        tokens = x.shape[0]
+        chosen, weights = ops.moe_route(x, self.router, self.correction, self.top, self.route_scale)
+        pairs = tokens * self.top
+        index = chosen.view(-1)
+        hidden = ops.indexed_linear(x, self.gate_up, index, pairs, in_div=self.top, gated=(self.limit, self.alpha))
+        down = ops.indexed_linear(hidden, self.down, index, pairs, out_dtype=torch.float32)
+        shared = None
+        if self.shared_gate_up is not None:
+            shared = ops.linear(ops.clamped_glu(ops.linear(x, self.shared_gate_up), self.shared_limit, self.alpha),
+                                self.shared_down)
+        return ops.moe_combine(down, weights, shared, self.runtime.dtype)

@@ -1,6 +1,9 @@
 """RMSNorm over the residual stream."""
 from __future__ import annotations
 
+from dataclasses import dataclass
+from typing import Optional
+
 import torch
 
 from .. import ops
@@ -9,24 +12,40 @@ from .base import Norm
 from .registry import NORMS
 
 
+@dataclass
+class NormedDelta:
+    """A sub-layer's output that still has to pass a norm of its own before it joins the stream: the block hands this
+    to the next norm's ``add_norm`` in place of a plain delta, and one kernel normalises it, adds it (with ``extra``,
+    a second 32-bit stream, when given) and normalises the stream for the next sub-layer."""
+    delta: Optional[torch.Tensor]
+    norm: Optional["RMSNorm"] = None
+    extra: Optional[torch.Tensor] = None
+
+
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
     """y = weight * x / sqrt(mean(x^2) + eps) (utils/layers.py:123-138): weight multiplies, it is not
-    (1 + weight); no bias.  Parameters: ``width``, ``eps``.  Fused with the residual add that precedes
+    (1 + weight); no bias.  Parameters: ``width``, ``eps``; ``tensor``: the weight's name behind the part's prefix
+    (default "weight"; "" when the prefix is the whole name).  Fused with the residual add that precedes
     it, as the reference's add_rms_norm (utils/fused_ops.py:145-155)."""
 
-    KNOWN_PARAMS = ("width", "eps")
+    KNOWN_PARAMS = ("width", "eps", "tensor")
 
     @classmethod
     def declare_weights(cls, params):
-        return {"weight": WeightDecl((params["width"],), NORM)}
+        return {params.get("tensor", "weight"): WeightDecl((params["width"],), NORM)}
 
     def __init__(self, params, weights, runtime):
         super().__init__(params, weights, runtime)
-        self.weight = weights["weight"].contiguous()
+        self.weight = weights[params.get("tensor", "weight")].contiguous()
         self.eps = float(params["eps"])
 
     def add_norm(self, residual, delta, rows=None, unscaled=False):
+        if isinstance(delta, NormedDelta):
+            post = delta.norm
+            return ops.normed_add_rmsnorm(residual, delta.delta, post.weight if post is not None else None,
+                                          post.eps if post is not None else 0.0, self.weight, self.eps,
+                                          extra=delta.extra, rows=rows, act_dtype=self.runtime.dtype)
         if isinstance(delta, ops.StreamSink):
             # the part in front added its result to the stream itself and, if asked, prepared this norm's input
             if delta.owner is not self or not delta.added:

@@ -3,7 +3,8 @@ hands them out in the model's dtype.
 
 Dtypes: matrices are kept in the compute dtype asked for (bfloat16 for serving, float32 for the
 32-bit path); a small tensor (a norm weight, say) that the checkpoint stores in 32-bit stays 32-bit,
-the kernels read it as such; integer tables become int32.  One ``WeightLoadError`` lists every missing tensor, every
+the kernels read it as such; integer tables become int32; tensors declared
+``WIDE`` (routers, per-head scalars) are widened to float32 in either path.  One ``WeightLoadError`` lists every missing tensor, every
 unexpected tensor and every wrong shape or dtype family; nothing is loaded partially.
 
 The reference loads module by module with ``load_state_dict(strict=True)`` (utils/model_loader.py:49-52),
@@ -17,7 +18,7 @@ from typing import Dict
 import torch
 
 from ..config.errors import WeightLoadError
-from .declare import MATRIX, TABLE, WeightDecl, declared_weights
+from .declare import MATRIX, TABLE, WIDE, WeightDecl, declared_weights
 from .reader import CheckpointReader
 
 _FLOAT_FAMILY = {"F64", "F32", "F16", "BF16"}
@@ -73,6 +74,8 @@ class CheckpointSource:
         tensor = self.reader.get(name)
         if declaration.kind == TABLE:
             return tensor.to(torch.int32).to(self.device)
+        if declaration.kind == WIDE:
+            return tensor.to(torch.float32).to(self.device)
         if declaration.kind != MATRIX and tensor.dtype == torch.float32:
             return tensor.to(self.device)  # a small tensor stored in 32-bit is not narrowed
         return tensor.to(self.dtype).to(self.device)

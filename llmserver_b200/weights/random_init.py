@@ -14,7 +14,7 @@ from typing import Dict
 
 import torch
 
-from .declare import MATRIX, NORM, TABLE, WeightDecl, declared_weights
+from .declare import MATRIX, NORM, TABLE, WIDE, WeightDecl, declared_weights
 
 
 def _tensor_seed(seed: int, name: str) -> int:
@@ -45,6 +45,9 @@ class RandomSource:
     def get(self, name: str) -> torch.Tensor:
         declaration = self.wanted[name]
         tensor = random_tensor(name, declaration, self.seed, self.device)
+        if declaration.kind == WIDE:
+            # what a bfloat16 checkpoint would hold, widened: the values do not depend on the compute dtype
+            return tensor.to(torch.bfloat16).to(torch.float32)
         return tensor if declaration.kind == TABLE else tensor.to(self.dtype)
 
 
