@@ -87,6 +87,10 @@ class GQAttention(Mixer):
         self.window = int(params["window"]) if params.get("window") else 0
         self.eps = float(params.get("eps", 0.0))
         self.value_dim = int(params.get("value_dim") or self.head_dim)
+        # keys and values of different sizes are rotated and cached by the kernel for split sizes
+        self.split = self.value_dim != self.head_dim
+        if self.split and params.get("qk_norm"):
+            raise ValueError("gqa_attention: per-head Q/K norms with values of another size than the keys are not supported")
         name = self.names(params)
         self.qkv = torch.cat([weights[name["q"]], weights[name["k"]], weights[name["v"]]], dim=0).contiguous()
         self.out = weights[name["o"]].contiguous()
@@ -94,10 +98,6 @@ class GQAttention(Mixer):
         self.k_norm = weights[name["k_norm"]].contiguous() if params.get("qk_norm") else None
         self.sinks = weights[name["sinks"]].to(torch.float32).contiguous() if params.get("sinks") else None
         self.inv_freq, self.rotary_dim, self.interleaved, self.magnitude = None, self.head_dim, False, 1.0
-        # keys and values of different sizes are rotated and cached by the kernel for split sizes
-        self.split = self.value_dim != self.head_dim
-        if self.split and params.get("qk_norm"):
-            raise ValueError("gqa_attention: per-head Q/K norms with values of another size than the keys are not supported")
 
     def attach(self, position):
         """``position``: None (no rotation) or an encoding with ``inv_freq`` (float32 [rotary_dim / 2] on the device)

@@ -416,8 +416,16 @@ def test_parts_refuse_what_they_cannot_do():
                "v_proj.weight": torch.zeros(16, 32, device=DEVICE), "o_proj.weight": torch.zeros(32, 32, device=DEVICE)}
     mixer = attention(good, weights, runtime)
     rotary = POSITION_ENCODINGS.get("rotary")
+    # a magnitude on cos and sin goes through the rotation kernel that has no per-head norm: refused with one
+    normed = attention({**good, "qk_norm": True}, {**weights, "q_norm.weight": torch.ones(16, device=DEVICE),
+                                                   "k_norm.weight": torch.ones(16, device=DEVICE)}, runtime)
     with pytest.raises(ValueError):
-        mixer.attach(rotary(dict(head_dim=16, theta=1e4, attention_factor=1.2), {}, runtime))
+        normed.attach(rotary(dict(head_dim=16, theta=1e4, attention_factor=1.2), {}, runtime))
+    scaled = attention(good, weights, runtime)
+    scaled.attach(rotary(dict(head_dim=16, theta=1e4, attention_factor=1.2), {}, runtime))
+    assert scaled.magnitude == 1.2 and scaled.split
+    with pytest.raises(ValueError):
+        attention({**good, "qk_norm": True, "value_dim": 8}, weights, runtime)       # nor with values of another size
     with pytest.raises(ValueError):
         mixer.attach(rotary(dict(head_dim=32, theta=1e4), {}, runtime))            # rotates more than a head holds
     with pytest.raises(ValueError):
