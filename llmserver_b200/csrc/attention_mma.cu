@@ -21,6 +21,11 @@
 // the P V sum follow utils/attention.py:186-198 with the running-max recurrence of
 // utils/attention.py:75-96.  Probabilities are rounded to bfloat16 for the P V product; the normaliser
 // is summed in 32-bit from the unrounded values.
+//
+// The cp.async kernels also come in a form for models whose attention weights have to stay 32-bit and whose softmax
+// has a sink (llm_attention_mma_sinks): values may have another size than keys (each 64 or 128), every probability
+// enters the P V product as the sum of two bfloat16 numbers (its rounding and the rounding of what that left over:
+// 16 significant bits, two MMAs instead of one), and exp(sink) joins the denominator once per row.
 #include "common.cuh"
 #include "tma.cuh"
 #include "tcgen05.cuh"
@@ -60,6 +65,8 @@ struct AttnParams {
     int slot_by_seq;         // scratch slots are counted by sequence instead of by the sequence's token index
     int* error_flag;         // 3: a bounded wait of the TMA decode kernel ran out; 5: a block-table entry names no page
                              // of the pool; 6: a context needs more splits than max_splits (may be null)
+    const float* sinks = nullptr;   // [Hq] or null: one more term exp(sinks[h]) in head h's softmax denominator (a score
+                                    // without key or value, neither scaled nor masked); cp.async kernels only
 };
 
 // A block-table entry as the kernels may follow it: an entry that names no page of the pool is reported and replaced
@@ -116,6 +123,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float low, float high) {
     __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
     return *reinterpret_cast<uint32_t*>(&pair);
 }
+// What rounding (low, high) to the bfloat16 pair `packed` left over, itself rounded to bfloat16.
+__device__ __forceinline__ uint32_t pack_bf16_rest(float low, float high, uint32_t packed) {
+    const float2 rounded = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&packed));
+    return pack_bf16(low - rounded.x, high - rounded.y);
+}
 
 // Thread-block cluster: a barrier over the threads of the cluster that have not exited, and a load from the shared
 // memory of another block of the cluster.
@@ -171,7 +183,7 @@ struct PageLayout {
 
 // Loads rows [first_key, first_key + 64) of one kv head into a swizzled shared tile; keys at or past
 // `end_key` are zero-filled.  All 128 threads take part.
-template <int D>
+template <int D, int DV = D>
 __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* k_tile, __nv_bfloat16* v_tile, const AttnParams& p,
                                              const int* table, int kv_head, int first_key, int end_key) {
     constexpr int kChunks = D / 8;                        // 16-byte chunks per row
@@ -191,18 +203,40 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* k_tile, __nv_bfloat1
         }
         const int destination = swizzled<D>(row, chunk);
         cp_async_16(smem_address(k_tile + destination), p.k_pages + offset, valid ? 16 : 0);
-        cp_async_16(smem_address(v_tile + destination), p.v_pages + offset, valid ? 16 : 0);
+        if (DV == D) cp_async_16(smem_address(v_tile + destination), p.v_pages + offset, valid ? 16 : 0);
+    }
+    if (DV != D) {      // values of another size than keys: rows of DV elements, walked the same way
+        constexpr int kValueChunks = DV / 8;
+        constexpr int kValuePerThread = kTileKeys * kValueChunks / kThreads;
+        constexpr int kValueRowsPerPass = kThreads / kValueChunks;
+        const int value_chunk = threadIdx.x % kValueChunks;
+        const int value_row0 = threadIdx.x / kValueChunks;
+#pragma unroll
+        for (int i = 0; i < kValuePerThread; ++i) {
+            const int row = value_row0 + i * kValueRowsPerPass;
+            const int key = first_key + row;
+            const bool valid = key < end_key;
+            size_t offset = 0;
+            if (valid) {
+                const int page = checked_page(p, table[key / p.page_size]);
+                offset = (((size_t)page * p.n_kv_heads + kv_head) * p.page_size + key % p.page_size) * DV + value_chunk * 8;
+            }
+            cp_async_16(smem_address(v_tile + swizzled<DV>(row, value_chunk)), p.v_pages + offset, valid ? 16 : 0);
+        }
     }
 }
 
 // One warp: 16 query rows against NT * 8 keys of a shared tile, starting at tile row `key_row`, whose
 // absolute key index is `key_index`.  Rows g = lane / 4 and g + 8 of the warp see keys in
 // [row_low[h], row_high[h]] (row_high < 0: the row does not exist).
-template <int D, int NT, class Layout = XorLayout<D>>
+//
+// DV: the size of a value row (V tiles are laid out by VLayout).  PRECISE: each probability enters the P V product as
+// two bfloat16 numbers, its rounding and the rounding of the rest, so the weights keep 16 significant bits.
+template <int D, int NT, class Layout = XorLayout<D>, int DV = D, bool PRECISE = false, class VLayout = Layout>
 __device__ __forceinline__ void warp_tile(const uint32_t (&q_frag)[D / 16][4], const __nv_bfloat16* k_tile,
                                           const __nv_bfloat16* v_tile, int key_row, int key_index,
                                           const int (&row_low)[2], const int (&row_high)[2], float scale_log2,
-                                          float (&o_acc)[D / 8][4], float (&row_max)[2], float (&row_sum)[2]) {
+                                          float (&o_acc)[DV / 8][4], float (&row_max)[2], float (&row_sum)[2]) {
     const int lane = threadIdx.x & 31;
     const int matrix = lane >> 3, matrix_row = lane & 7;
     float s_acc[NT][4];
@@ -250,7 +284,7 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&q_frag)[D / 16][4], c
         row_sum[h] *= correction[h];
     }
 #pragma unroll
-    for (int n = 0; n < D / 8; ++n) {
+    for (int n = 0; n < DV / 8; ++n) {
         o_acc[n][0] *= correction[0];
         o_acc[n][1] *= correction[0];
         o_acc[n][2] *= correction[1];
@@ -274,13 +308,24 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&q_frag)[D / 16][4], c
         a[1] = pack_bf16(s_acc[2 * kk][2], s_acc[2 * kk][3]);
         a[2] = pack_bf16(s_acc[2 * kk + 1][0], s_acc[2 * kk + 1][1]);
         a[3] = pack_bf16(s_acc[2 * kk + 1][2], s_acc[2 * kk + 1][3]);
+        uint32_t rest[4];
+        if (PRECISE) {
+            rest[0] = pack_bf16_rest(s_acc[2 * kk][0], s_acc[2 * kk][1], a[0]);
+            rest[1] = pack_bf16_rest(s_acc[2 * kk][2], s_acc[2 * kk][3], a[1]);
+            rest[2] = pack_bf16_rest(s_acc[2 * kk + 1][0], s_acc[2 * kk + 1][1], a[2]);
+            rest[3] = pack_bf16_rest(s_acc[2 * kk + 1][2], s_acc[2 * kk + 1][3], a[3]);
+        }
 #pragma unroll
-        for (int j = 0; j < D / 16; ++j) {
+        for (int j = 0; j < DV / 16; ++j) {
             uint32_t b[4];
             const int row = key_row + kk * 16 + (matrix & 1) * 8 + matrix_row;
-            ldmatrix_x4_trans(b, smem_address(v_tile + Layout::at(row, 2 * j + (matrix >> 1))));
+            ldmatrix_x4_trans(b, smem_address(v_tile + VLayout::at(row, 2 * j + (matrix >> 1))));
             mma_bf16(o_acc[2 * j], a, b[0], b[1]);
             mma_bf16(o_acc[2 * j + 1], a, b[2], b[3]);
+            if (PRECISE) {
+                mma_bf16(o_acc[2 * j], rest, b[0], b[1]);
+                mma_bf16(o_acc[2 * j + 1], rest, b[2], b[3]);
+            }
         }
     }
 }
@@ -288,13 +333,14 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&q_frag)[D / 16][4], c
 // ------------------------------------------------------------------------------------------------
 // portions of prompts
 // ------------------------------------------------------------------------------------------------
-template <int D>
+template <int D, int DV = D, bool PRECISE = false>
 __global__ void __launch_bounds__(kThreads) attention_portions_kernel(const AttnParams p) {
     pdl_trigger();   // let the next kernel start launching
     pdl_wait();      // everything before this kernel in the stream is complete and visible
     extern __shared__ __align__(16) unsigned char shared_raw[];
     __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(shared_raw);   // [64][D]
-    __nv_bfloat16* kv_tiles = q_tile + kTileRows * D;                        // [2 stages][K, V][64][D]
+    __nv_bfloat16* kv_tiles = q_tile + kTileRows * D;                        // [2 stages][K [64][D], V [64][DV]]
+    constexpr int kStage = kTileKeys * (D + DV);
 
     const int group = p.n_q_heads / p.n_kv_heads;
     const int kv_head = blockIdx.y;
@@ -341,7 +387,7 @@ __global__ void __launch_bounds__(kThreads) attention_portions_kernel(const Attn
     const int first_tile_key = (low_key / kTileKeys) * kTileKeys;
     const int n_tiles = (high_key - first_tile_key) / kTileKeys + 1;
 
-    load_kv_tile<D>(kv_tiles, kv_tiles + kTileKeys * D, p, table, kv_head, first_tile_key, context);
+    load_kv_tile<D, DV>(kv_tiles, kv_tiles + kTileKeys * D, p, table, kv_head, first_tile_key, context);
     cp_async_commit();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -359,9 +405,9 @@ __global__ void __launch_bounds__(kThreads) attention_portions_kernel(const Attn
             row_low[h] = 0;
         }
     }
-    float o_acc[D / 8][4];
+    float o_acc[DV / 8][4];
 #pragma unroll
-    for (int n = 0; n < D / 8; ++n)
+    for (int n = 0; n < DV / 8; ++n)
 #pragma unroll
         for (int i = 0; i < 4; ++i) o_acc[n][i] = 0.0f;
     float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
@@ -370,11 +416,11 @@ __global__ void __launch_bounds__(kThreads) attention_portions_kernel(const Attn
 
     for (int it = 0; it < n_tiles; ++it) {
         const int stage = it & 1;
-        __nv_bfloat16* k_tile = kv_tiles + stage * 2 * kTileKeys * D;
+        __nv_bfloat16* k_tile = kv_tiles + stage * kStage;
         __nv_bfloat16* v_tile = k_tile + kTileKeys * D;
         if (it + 1 < n_tiles) {
-            __nv_bfloat16* next_k = kv_tiles + (stage ^ 1) * 2 * kTileKeys * D;
-            load_kv_tile<D>(next_k, next_k + kTileKeys * D, p, table, kv_head, first_tile_key + (it + 1) * kTileKeys, context);
+            __nv_bfloat16* next_k = kv_tiles + (stage ^ 1) * kStage;
+            load_kv_tile<D, DV>(next_k, next_k + kTileKeys * D, p, table, kv_head, first_tile_key + (it + 1) * kTileKeys, context);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -392,7 +438,7 @@ __global__ void __launch_bounds__(kThreads) attention_portions_kernel(const Attn
         const int tile_key = first_tile_key + it * kTileKeys;
         // a warp whose rows all end before this tile has nothing to add (the causal upper triangle)
         if (tile_key <= warp_high)
-            warp_tile<D, 8>(q_frag, k_tile, v_tile, 0, tile_key, row_low, row_high, p.scale_log2, o_acc, row_max, row_sum);
+            warp_tile<D, 8, XorLayout<D>, DV, PRECISE, XorLayout<DV>>(q_frag, k_tile, v_tile, 0, tile_key, row_low, row_high, p.scale_log2, o_acc, row_max, row_sum);
         __syncthreads();   // the stage is overwritten by the load issued in the next iteration
     }
 
@@ -405,10 +451,17 @@ __global__ void __launch_bounds__(kThreads) attention_portions_kernel(const Attn
         total += __shfl_xor_sync(0xffffffffu, total, 2);
         const int r = first_row + warp * 16 + g + 8 * h;
         if (r >= n_rows) continue;
-        const float inverse = 1.0f / total;
-        __nv_bfloat16* dst = p.out + (size_t)(token0 + r / group) * p.n_q_heads * D + (size_t)(kv_head * group + r % group) * D;
+        float shrink = 1.0f;
+        if (p.sinks) {      // the sink joins the denominator; against a larger sink the sums shrink
+            const float sink = p.sinks[kv_head * group + r % group] * kLog2e;
+            const float new_max = fmaxf(row_max[h], sink);
+            shrink = exp2f(row_max[h] - new_max);
+            total = total * shrink + exp2f(sink - new_max);
+        }
+        const float inverse = shrink / total;
+        __nv_bfloat16* dst = p.out + (size_t)(token0 + r / group) * p.n_q_heads * DV + (size_t)(kv_head * group + r % group) * DV;
 #pragma unroll
-        for (int n = 0; n < D / 8; ++n) {
+        for (int n = 0; n < DV / 8; ++n) {
             const uint32_t packed = pack_bf16(o_acc[n][2 * h] * inverse, o_acc[n][2 * h + 1] * inverse);
             *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * t) = packed;
         }
@@ -419,19 +472,20 @@ __global__ void __launch_bounds__(kThreads) attention_portions_kernel(const Attn
 // decode: one token per sequence, keys split across blocks
 // ------------------------------------------------------------------------------------------------
 // A decode row whose sequence holds no token (context_len <= 0) has nothing to attend to: its output is zero.
-template <int D>
+template <int D>      // D: the size of a value row
 __device__ __forceinline__ void zero_output(const AttnParams& p, int token, int kv_head, int group) {
     for (int index = threadIdx.x; index < group * D; index += blockDim.x)
         p.out[(size_t)token * p.n_q_heads * D + (size_t)(kv_head * group) * D + index] = __float2bfloat16_rn(0.0f);
 }
 
-template <int D>
+template <int D, int DV = D, bool PRECISE = false>
 __global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnParams p) {
     pdl_trigger();   // let the next kernel start launching
     pdl_wait();      // everything before this kernel in the stream is complete and visible
     extern __shared__ __align__(16) unsigned char shared_raw[];
     __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(shared_raw);   // [16][D]
-    __nv_bfloat16* kv_tiles = q_tile + 16 * D;                               // [2 stages][K, V][64][D]
+    __nv_bfloat16* kv_tiles = q_tile + 16 * D;                               // [2 stages][K [64][D], V [64][DV]]
+    constexpr int kStage = kTileKeys * (D + DV);
 
     const int seq = blockIdx.z, kv_head = blockIdx.y, split = blockIdx.x;
     const int token = p.q_start[seq];
@@ -444,7 +498,7 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnPa
     const int split_len = split_length(p, context - first_key);
     const int n_splits = (context - first_key + split_len - 1) / split_len;
     if (n_splits > p.max_splits && split == 0 && kv_head == 0 && threadIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, 6);
-    if (context <= 0 && split == 0) zero_output<D>(p, token, kv_head, group);     // nothing to attend to
+    if (context <= 0 && split == 0) zero_output<DV>(p, token, kv_head, group);     // nothing to attend to
     if (split >= n_splits) return;
     const int split_begin = first_key + split * split_len;
     const int split_end = min(split_begin + split_len, context);
@@ -461,7 +515,7 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnPa
             cp_async_16(smem_address(q_tile + swizzled<D>(row, chunk)), src, valid ? 16 : 0);
         }
     }
-    load_kv_tile<D>(kv_tiles, kv_tiles + kTileKeys * D, p, table, kv_head, split_begin, split_end);
+    load_kv_tile<D, DV>(kv_tiles, kv_tiles + kTileKeys * D, p, table, kv_head, split_begin, split_end);
     cp_async_commit();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -473,9 +527,9 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnPa
         row_high[h] = exists ? position : -1;
         row_low[h] = low_key;
     }
-    float o_acc[D / 8][4];
+    float o_acc[DV / 8][4];
 #pragma unroll
-    for (int n = 0; n < D / 8; ++n)
+    for (int n = 0; n < DV / 8; ++n)
 #pragma unroll
         for (int i = 0; i < 4; ++i) o_acc[n][i] = 0.0f;
     float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
@@ -483,11 +537,11 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnPa
 
     for (int it = 0; it < n_tiles; ++it) {
         const int stage = it & 1;
-        __nv_bfloat16* k_tile = kv_tiles + stage * 2 * kTileKeys * D;
+        __nv_bfloat16* k_tile = kv_tiles + stage * kStage;
         __nv_bfloat16* v_tile = k_tile + kTileKeys * D;
         if (it + 1 < n_tiles) {
-            __nv_bfloat16* next_k = kv_tiles + (stage ^ 1) * 2 * kTileKeys * D;
-            load_kv_tile<D>(next_k, next_k + kTileKeys * D, p, table, kv_head, split_begin + (it + 1) * kTileKeys, split_end);
+            __nv_bfloat16* next_k = kv_tiles + (stage ^ 1) * kStage;
+            load_kv_tile<D, DV>(next_k, next_k + kTileKeys * D, p, table, kv_head, split_begin + (it + 1) * kTileKeys, split_end);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -505,49 +559,53 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnPa
         // each warp takes 16 of the tile's 64 keys
         const int key_index = split_begin + it * kTileKeys + warp * 16;
         if (key_index < split_end)
-            warp_tile<D, 2>(q_frag, k_tile, v_tile, warp * 16, key_index, row_low, row_high, p.scale_log2, o_acc, row_max, row_sum);
+            warp_tile<D, 2, XorLayout<D>, DV, PRECISE, XorLayout<DV>>(q_frag, k_tile, v_tile, warp * 16, key_index, row_low, row_high, p.scale_log2, o_acc, row_max, row_sum);
         __syncthreads();
     }
 
     // merge the four warps through shared memory (the K/V stages are free now)
-    float* merge = reinterpret_cast<float*>(kv_tiles);        // [4 warps][16 rows][D + 2]
+    float* merge = reinterpret_cast<float*>(kv_tiles);        // [4 warps][16 rows][DV + 2]
     const int t = lane & 3;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         float total = row_sum[h];
         total += __shfl_xor_sync(0xffffffffu, total, 1);
         total += __shfl_xor_sync(0xffffffffu, total, 2);
-        float* row = merge + ((size_t)warp * 16 + g + 8 * h) * (D + 2);
+        float* row = merge + ((size_t)warp * 16 + g + 8 * h) * (DV + 2);
 #pragma unroll
-        for (int n = 0; n < D / 8; ++n) {
+        for (int n = 0; n < DV / 8; ++n) {
             row[n * 8 + 2 * t] = o_acc[n][2 * h];
             row[n * 8 + 2 * t + 1] = o_acc[n][2 * h + 1];
         }
         if (t == 0) {
-            row[D] = row_max[h];
-            row[D + 1] = total;
+            row[DV] = row_max[h];
+            row[DV + 1] = total;
         }
     }
     __syncthreads();
-    for (int index = threadIdx.x; index < group * D; index += kThreads) {
-        const int r = index / D, d = index % D;
+    for (int index = threadIdx.x; index < group * DV; index += kThreads) {
+        const int r = index / DV, d = index % DV;
         float best = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) best = fmaxf(best, merge[((size_t)w * 16 + r) * (D + 2) + D]);
-        float numerator = 0.0f, denominator = 0.0f;
+        for (int w = 0; w < 4; ++w) best = fmaxf(best, merge[((size_t)w * 16 + r) * (DV + 2) + DV]);
+        const int head = kv_head * group + r;
+        // the sink counts once per row: the first split takes it in, as one more score without a value
+        const bool with_sink = p.sinks != nullptr && split == 0;
+        const float sink = with_sink ? p.sinks[head] * kLog2e : -INFINITY;
+        best = fmaxf(best, sink);
+        float numerator = 0.0f, denominator = with_sink ? exp2f(sink - best) : 0.0f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            const float* row = merge + ((size_t)w * 16 + r) * (D + 2);
-            const float weight = row[D] == -INFINITY ? 0.0f : exp2f(row[D] - best);
+            const float* row = merge + ((size_t)w * 16 + r) * (DV + 2);
+            const float weight = row[DV] == -INFINITY ? 0.0f : exp2f(row[DV] - best);
             numerator += row[d] * weight;
-            denominator += row[D + 1] * weight;
+            denominator += row[DV + 1] * weight;
         }
-        const int head = kv_head * group + r;
         if (n_splits == 1) {
-            p.out[(size_t)token * p.n_q_heads * D + (size_t)head * D + d] = __float2bfloat16_rn(numerator / denominator);
+            p.out[(size_t)token * p.n_q_heads * DV + (size_t)head * DV + d] = __float2bfloat16_rn(numerator / denominator);
         } else {
             const size_t slot = ((size_t)(p.slot_by_seq ? seq : token) * p.n_q_heads + head) * p.max_splits + split;
-            p.partial_out[slot * D + d] = numerator / denominator;
+            p.partial_out[slot * DV + d] = numerator / denominator;
             if (d == 0) {
                 p.partial_ml[slot * 2] = best;
                 p.partial_ml[slot * 2 + 1] = denominator;
@@ -881,24 +939,42 @@ __global__ void attention_decode_merge_kernel(const AttnParams p) {
     }
 }
 
-template <int D>
+template <int D, int DV = D, bool PRECISE = false>
 int launch_portions(const AttnParams& p, int total_tiles, cudaStream_t stream) {
-    const size_t shared = (size_t)(kTileRows * D + 4 * kTileKeys * D) * sizeof(__nv_bfloat16);
-    if (int limit_status = llm_raise_shared_limit(reinterpret_cast<const void*>(attention_portions_kernel<D>), shared, "attention_portions")) return limit_status;
+    const size_t shared = (size_t)(kTileRows * D + 2 * kTileKeys * (D + DV)) * sizeof(__nv_bfloat16);
+    if (int limit_status = llm_raise_shared_limit(reinterpret_cast<const void*>(attention_portions_kernel<D, DV, PRECISE>), shared, "attention_portions")) return limit_status;
     dim3 grid(total_tiles, p.n_kv_heads);
-    llm_launch(attention_portions_kernel<D>, grid, kThreads, shared, stream, p);
+    llm_launch(attention_portions_kernel<D, DV, PRECISE>, grid, kThreads, shared, stream, p);
     return llm_check_launch("attention_portions");
 }
 
-template <int D>
+template <int D, int DV = D, bool PRECISE = false>
 int launch_decode_cp_async(const AttnParams& p, cudaStream_t stream) {
-    size_t shared = (size_t)(16 * D + 4 * kTileKeys * D) * sizeof(__nv_bfloat16);
-    const size_t merge = (size_t)4 * 16 * (D + 2) * sizeof(float) + 16 * D * sizeof(__nv_bfloat16);
+    size_t shared = (size_t)(16 * D + 2 * kTileKeys * (D + DV)) * sizeof(__nv_bfloat16);
+    const size_t merge = (size_t)4 * 16 * (DV + 2) * sizeof(float) + 16 * D * sizeof(__nv_bfloat16);
     if (merge > shared) shared = merge;
-    if (int limit_status = llm_raise_shared_limit(reinterpret_cast<const void*>(attention_decode_kernel<D>), shared, "attention_decode")) return limit_status;
+    if (int limit_status = llm_raise_shared_limit(reinterpret_cast<const void*>(attention_decode_kernel<D, DV, PRECISE>), shared, "attention_decode")) return limit_status;
     dim3 grid(p.max_splits, p.n_kv_heads, p.n_seqs);
-    llm_launch(attention_decode_kernel<D>, grid, kThreads, shared, stream, p);
+    llm_launch(attention_decode_kernel<D, DV, PRECISE>, grid, kThreads, shared, stream, p);
     return llm_check_launch("attention_decode");
+}
+
+// The form with 32-bit-grade attention weights, sinks and a value size of its own: the cp.async kernels, splits merged
+// by the merge kernel.
+template <int D, int DV>
+int launch_precise(const AttnParams& p, int run_portions, int total_tiles, int run_decode, cudaStream_t stream) {
+    int status = LLM_OK;
+    if (run_portions && total_tiles > 0) status = launch_portions<D, DV, true>(p, total_tiles, stream);
+    if (status != LLM_OK || !run_decode) return status;
+    if (p.max_splits > 1 && (p.partial_out == nullptr || p.partial_ml == nullptr)) {
+        llm_set_error("attention_decode: %d splits need the scratch buffers for partial results", p.max_splits);
+        return LLM_REFUSED;
+    }
+    status = launch_decode_cp_async<D, DV, true>(p, stream);
+    if (status != LLM_OK || p.max_splits <= 1) return status;
+    dim3 merge_grid(p.n_q_heads, p.n_seqs);
+    llm_launch(attention_decode_merge_kernel<DV>, merge_grid, DV < 128 ? DV : 128, 0, stream, p);
+    return llm_check_launch("attention_decode_merge");
 }
 
 template <int D>
@@ -1189,4 +1265,69 @@ LLM_EXPORT int llm_attention_decode_noalloc_status(cudaStream_t stream) {
         return -(int)status;
     }
     return value;
+}
+
+
+// Sizes the form with sinks takes: keys and values of 64 or 128 elements each, groups of up to 16 heads.
+LLM_EXPORT int llm_attention_mma_sinks_supports(int head_dim, int value_dim, int n_q_heads, int n_kv_heads) {
+    if ((head_dim != 64 && head_dim != 128) || (value_dim != 64 && value_dim != 128)) return 0;
+    if (n_kv_heads <= 0 || n_q_heads % n_kv_heads) return 0;
+    return n_q_heads / n_kv_heads <= 16;
+}
+
+// Attention whose weights keep 16 significant bits in the P V product (see PRECISE above), with value heads of
+// `value_dim` elements and, with `sinks` (float32 [Hq], may be null), one more term exp(sinks[h]) in every row's
+// denominator.  The other arguments as for llm_attention_mma; out is [N, Hq * value_dim].
+LLM_EXPORT int llm_attention_mma_sinks(const void* q, int q_stride, const void* k_pages, const void* v_pages,
+                                       const int* block_tables, int max_blocks, const int* q_start, const int* context_len,
+                                       void* out, int n_seqs, int n_q_heads, int n_kv_heads, int head_dim, int value_dim,
+                                       int page_size, int num_pages, float scale, int window, const float* sinks,
+                                       int run_portions, int total_tiles, int run_decode, int split_len, int max_splits,
+                                       float* partial_out, float* partial_ml, int* error_flag, cudaStream_t stream) {
+    if (!llm_attention_mma_sinks_supports(head_dim, value_dim, n_q_heads, n_kv_heads)) {
+        llm_set_error("attention_mma_sinks: keys of %d and values of %d with %d/%d heads are not supported (64 or 128 each, "
+                      "group <= 16)", head_dim, value_dim, n_q_heads, n_kv_heads);
+        return LLM_REFUSED;
+    }
+    if (run_decode && (split_len == 0 || (split_len > 0 && split_len % kTileKeys) || max_splits <= 0 || -split_len > max_splits)) {
+        llm_set_error("attention_mma_sinks: split_len %d must be a positive multiple of %d, or minus a number of parts up to max_splits", split_len, kTileKeys);
+        return LLM_REFUSED;
+    }
+    if (n_seqs > 65535 || n_kv_heads > 65535 || num_pages <= 0) {
+        llm_set_error("attention_mma_sinks: at most 65535 sequences and kv heads per launch and a pool of at least one page");
+        return LLM_REFUSED;
+    }
+    AttnParams p;
+    p.q = (const __nv_bfloat16*)q;
+    p.q_stride = q_stride;
+    p.k_pages = (const __nv_bfloat16*)k_pages;
+    p.v_pages = (const __nv_bfloat16*)v_pages;
+    p.block_tables = block_tables;
+    p.max_blocks = max_blocks;
+    p.num_pages = num_pages;
+    p.slot_by_seq = 0;
+    p.cluster_merge = 0;
+    p.old_keys_settled = 0;
+    p.q_start = q_start;
+    p.context_len = context_len;
+    p.out = (__nv_bfloat16*)out;
+    p.n_seqs = n_seqs;
+    p.n_q_heads = n_q_heads;
+    p.n_kv_heads = n_kv_heads;
+    p.page_size = page_size;
+    p.scale_log2 = scale * kLog2e;
+    p.window = window;
+    p.skip_single = run_decode;
+    p.split_len = split_len;
+    p.max_splits = max_splits;
+    p.partial_out = partial_out;
+    p.partial_ml = partial_ml;
+    p.error_flag = error_flag;
+    p.sinks = sinks;
+    if (head_dim == 64) {
+        return value_dim == 64 ? launch_precise<64, 64>(p, run_portions, total_tiles, run_decode, stream)
+                               : launch_precise<64, 128>(p, run_portions, total_tiles, run_decode, stream);
+    }
+    return value_dim == 64 ? launch_precise<128, 64>(p, run_portions, total_tiles, run_decode, stream)
+                           : launch_precise<128, 128>(p, run_portions, total_tiles, run_decode, stream);
 }

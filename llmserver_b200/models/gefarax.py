@@ -49,7 +49,7 @@ def gefarax_spec(config: GefaraxConfig) -> ModelSpec:
         mixer = layer.mixer
         attention = PartSpec.of("gqa_attention", hidden=config.width, heads=int(mixer["heads"]), kv_heads=int(mixer["kv_heads"]),
                                 head_dim=int(mixer["dim"]), value_dim=int(mixer["vdim"]), scale=float(mixer["scale"]),
-                                sinks=True, names=ATTENTION_NAMES)
+                                sinks=True, precise_weights=True, names=ATTENTION_NAMES)
         feed_forward = None
         if layer.mlp is not None:
             mlp = layer.mlp

@@ -435,17 +435,22 @@ def qkv_projection(x, weight: torch.Tensor, q_weight: Optional[torch.Tensor], k_
 
 def attention(qkv: torch.Tensor, batch, block_tables: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
               n_q_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int = 0,
-              value_dim: Optional[int] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+              value_dim: Optional[int] = None, sinks: Optional[torch.Tensor] = None, precise: bool = False) -> torch.Tensor:
     """Attention of a step's tokens over the paged cache; ``qkv`` is the packed projection whose Q
     heads have been normalised and rotated in place.  Chooses the kernel by dtype, head size and the
     shape of the batch; every choice computes the same function.  ``value_dim`` (default: head_dim) and ``sinks`` as
-    in ``attention_generic``."""
+    in ``attention_generic``.  ``precise``: the attention weights may not be rounded to bfloat16 on their way into the
+    P V product (the tensor-core kernels then carry each as two bfloat16 numbers)."""
     value_dim = head_dim if value_dim is None else int(value_dim)
     q_stride = (n_q_heads + n_kv_heads) * head_dim + n_kv_heads * value_dim
-    if qkv.dtype == torch.bfloat16 and value_dim == head_dim and sinks is None:
+    if qkv.dtype == torch.bfloat16:
         from . import attention_bf16
-        result = attention_bf16.try_attention(qkv, q_stride, batch, block_tables, k_pages, v_pages, n_q_heads,
-                                              n_kv_heads, head_dim, scale, window)
+        if value_dim == head_dim and sinks is None and not precise:
+            result = attention_bf16.try_attention(qkv, q_stride, batch, block_tables, k_pages, v_pages, n_q_heads,
+                                                  n_kv_heads, head_dim, scale, window)
+        else:
+            result = attention_bf16.try_attention_precise(qkv, q_stride, batch, block_tables, k_pages, v_pages, n_q_heads,
+                                                          n_kv_heads, head_dim, value_dim, scale, window, sinks)
         if result is not None:
             return result
     return attention_generic(qkv, q_stride, k_pages, v_pages, block_tables, batch.seq_of_token, batch.positions,

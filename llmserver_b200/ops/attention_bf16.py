@@ -181,3 +181,36 @@ def try_attention(qkv, q_stride, batch, block_tables, k_pages, v_pages, n_q_head
          0 if partial_ml is None else partial_ml.data_ptr(), int(EARLY_KEYS and getattr(batch, "keys_settled", False)), flag,
          stream_handle())
     return out
+
+
+def try_attention_precise(qkv, q_stride, batch, block_tables, k_pages, v_pages, n_q_heads, n_kv_heads, head_dim, value_dim,
+                          scale, window, sinks):
+    """The tensor-core kernels in the form that keeps attention weights at 16 significant bits through the P V product,
+    takes value heads of another size than key heads and adds exp(sinks[h]) to each softmax denominator; None when the
+    sizes are not ones it takes (64 or 128 each)."""
+    if not library().llm_attention_mma_sinks_supports(head_dim, value_dim, n_q_heads, n_kv_heads):
+        return None
+    check(qkv, "qkv", torch.bfloat16)
+    check(k_pages, "k pages", torch.bfloat16, head_dim)
+    check(v_pages, "v pages", torch.bfloat16, value_dim)
+    check(block_tables, "block_tables", torch.int32)
+    if sinks is not None:
+        check(sinks, "sinks", torch.float32, n_q_heads)
+    run_portions, tiles, run_decode, split_len, max_splits = plan(batch, n_q_heads // n_kv_heads, n_kv_heads, qkv.device)
+    out = torch.empty((batch.n_tokens, n_q_heads * value_dim), dtype=torch.bfloat16, device=qkv.device)
+    partial_out = partial_ml = None
+    if run_decode and max_splits > 1:
+        key = ("attention_mma_scratch", n_q_heads, value_dim, max_splits)
+        scratch = batch.scratch.get(key)
+        if scratch is None:
+            scratch = (torch.empty((batch.n_tokens, n_q_heads, max_splits, value_dim), dtype=torch.float32, device=qkv.device),
+                       torch.empty((batch.n_tokens, n_q_heads, max_splits, 2), dtype=torch.float32, device=qkv.device))
+            batch.scratch[key] = scratch
+        partial_out, partial_ml = scratch
+    call("llm_attention_mma_sinks", qkv.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(), block_tables.data_ptr(),
+         block_tables.shape[-1], batch.q_start.data_ptr(), batch.context_len.data_ptr(), out.data_ptr(), batch.n_seqs,
+         n_q_heads, n_kv_heads, head_dim, value_dim, k_pages.shape[2], k_pages.shape[0], float(scale), int(window),
+         0 if sinks is None else sinks.data_ptr(), int(run_portions), tiles, int(run_decode), split_len, max_splits,
+         0 if partial_out is None else partial_out.data_ptr(), 0 if partial_ml is None else partial_ml.data_ptr(),
+         wait_error_flag(qkv.device).data_ptr(), stream_handle())
+    return out

@@ -32,6 +32,8 @@ SIGNATURES = {
     "llm_clamped_glu": [_P, _P, _I, _I, _F, _F, _I, _S],
     "llm_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _S],
     "llm_attention_mma_supports": [_I, _I, _I],
+    "llm_attention_mma_sinks_supports": [_I, _I, _I, _I],
+    "llm_attention_mma_sinks": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _I, _I, _I, _I, _P, _P, _P, _S],
     "llm_attention_prefill_tcgen05_supports": [_I, _I, _I, _I],
     "llm_attention_prefill_tcgen05": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _S],
     "llm_attention_prefill_wide_supports": [_I, _I, _I, _I],

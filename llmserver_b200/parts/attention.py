@@ -27,7 +27,8 @@ class GQAttention(Mixer):
     epilogue nor score capping, and say so instead of computing without them.  ``value_dim``: the size of a value
     head where it differs from ``head_dim`` (the output projection then reads heads * value_dim columns).  ``sinks``
     (bool): a learned number per query head joins each softmax's denominator as exp(sink), without a key or a value,
-    neither scaled nor masked.  ``names``: pairs (role, tensor name behind the prefix) for checkpoints that call the
+    neither scaled nor masked.  ``precise_weights`` (bool): the design wants its attention weights in 32-bit, so the
+    bfloat16 kernels may not round them to 8 bits for the P V product.  ``names``: pairs (role, tensor name behind the prefix) for checkpoints that call the
     tensors otherwise; roles are q, k, v, o, q_norm, k_norm, sinks.
 
     How positions are encoded comes from the position encoding the layer names (``attach``): its inverse
@@ -37,7 +38,7 @@ class GQAttention(Mixer):
     refused.  The same kernel serves heads whose values have another size than their keys."""
 
     KNOWN_PARAMS = ("hidden", "heads", "kv_heads", "head_dim", "scale", "qk_norm", "eps", "window", "bias", "softcap",
-                    "value_dim", "sinks", "names")
+                    "value_dim", "sinks", "names", "precise_weights")
     NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
              "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "sinks": "sinks"}
 
@@ -142,5 +143,6 @@ class GQAttention(Mixer):
                                      tables, cache.k_pages, cache.v_pages, self.heads, self.kv_heads, self.head_dim, self.eps,
                                      cache.writes, batch.error_flag, self.rotary_dim, self.interleaved)
         attended = ops.attention(qkv, batch, tables, cache.k_pages, cache.v_pages, self.heads, self.kv_heads,
-                                 self.head_dim, self.scale, self.window, value_dim=self.value_dim, sinks=self.sinks)
+                                 self.head_dim, self.scale, self.window, value_dim=self.value_dim, sinks=self.sinks,
+                                 precise=bool(self.params.get("precise_weights")))
         return ops.linear(attended, self.out, sink=sink)
