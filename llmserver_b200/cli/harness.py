@@ -134,7 +134,9 @@ def prefill_flops(config, layers: int, tokens: int) -> float:
 class Harness:
     """Model, cache and step function sized for the largest batch, reused by every measurement."""
 
-    def __init__(self, layers: int, max_batch: int, seed: int = 0, shape: str = "8b"):
+    def __init__(self, layers: int, max_batch: int, seed: int = 0, shape: str = "8b", config=None):
+        """``config``: a typed configuration of any registered architecture (then ``layers`` and ``shape`` only label the
+        run); default: the Qwen3 ``shape`` with ``layers`` layers."""
         import torch
         from llmserver_b200.cache import CacheManager
         from llmserver_b200.config import Qwen3Config
@@ -142,17 +144,26 @@ class Harness:
         from llmserver_b200.models import random_model
 
         self.torch = torch
-        raw = dict(SHAPES[shape], num_hidden_layers=layers)
-        self.config = Qwen3Config.from_dict(raw)
+        if config is None:
+            config = Qwen3Config.from_dict(dict(SHAPES[shape], num_hidden_layers=layers))
+        self.config = config
         self.layers = layers
         self.model = random_model(self.config, seed, "bfloat16", "cuda:0")
         pages = max_batch * (CONTEXT // PAGE_SIZE) + 8     # the reference benchmark's sizing rule
         self.cache = CacheManager(self.model.cache_needs(), PAGE_SIZE, pages, num_slots=max_batch, prefix_sharing=False)
         self.cache.materialize(self.model.runtime.device, self.model.runtime.dtype)
         for group in self.cache.groups:     # contents do not change the timing; avoid an all-zero cache anyway
-            group.storage.normal_(0.0, 0.5)
+            group.key_storage.normal_(0.0, 0.5)
+            group.value_storage.normal_(0.0, 0.5)
         self.step_function = StepFunction(self.model, self.cache)
         self.generator = torch.Generator().manual_seed(seed)
+
+    def close(self):
+        """Gives the device memory back (for runs that measure several models one after the other)."""
+        self.step_function = self.cache = self.model = None
+        import gc
+        gc.collect()
+        self.torch.cuda.empty_cache()
 
     def tokens(self, count: int):
         return self.torch.randint(0, self.config.vocab_size, (count,), generator=self.generator).tolist()
@@ -275,3 +286,68 @@ class Harness:
                 "host_phases_ms": ", ".join(f"{name} {phases[name]:.3f}" for name in ("schedule", "pack_copy", "launch", "read_back", "accept"))}
 
 
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Gefarax beside the dense decoder at equal size
+# ---------------------------------------------------------------------------------------------------------------------
+def _gefarax_size(width, heads, kv_heads, dim, vdim, experts, top, ff, shared_ff):
+    return dict(width=width, heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, experts=experts, top=top, ff=ff, shared_ff=shared_ff)
+
+
+# Layer sizes that resemble served models: a small one with heads of 64, one whose active feed-forward and attention
+# equal the Qwen3-8B shape's, and one with many small experts and value heads half the size of its key heads.
+GEFARAX_SIZES = {
+    "w2048-h64": _gefarax_size(2048, 32, 8, 64, 64, 32, 4, 768, 768),
+    "w4096-h128": _gefarax_size(4096, 32, 8, 128, 128, 64, 6, 1792, 1536),
+    "w4096-v64": _gefarax_size(4096, 64, 8, 128, 64, 128, 4, 1024, 2048),
+}
+COMPARE_VOCAB = 151936
+
+
+def gefarax_config(size: dict, layers: int):
+    """A Gefarax configuration of ``layers`` equal layers of the given sizes (no loop), with the constants of a model
+    stretched from 4096 to 32768 positions."""
+    from llmserver_b200.config import GefaraxConfig
+    layer = {"type": "attention",
+             "mixer": {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": size["dim"], "vdim": size["vdim"],
+                       "scale": size["dim"] ** -0.5,
+                       "rot": {"base": 150000.0, "dims": size["dim"],
+                               "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+             "mlp": {"kind": "moe", "router": {"experts": size["experts"], "top": size["top"], "scale": 1.0},
+                     "expert": {"ff": size["ff"], "limit": 7.0}, "shared": {"ff": size["shared_ff"], "limit": 7.0}}}
+    return GefaraxConfig.from_dict({"architecture": "Gefarax", "vocab": COMPARE_VOCAB, "width": size["width"], "norm": {"eps": 1e-6},
+                                    "layers": [layer] * layers, "loop": None})
+
+
+def dense_twin_config(size: dict, layers: int):
+    """The dense decoder of equal size: the same width, heads and key size, and a feed-forward as wide as the experts a
+    token uses plus the shared one."""
+    from llmserver_b200.config import Qwen3Config
+    raw = dict(_qwen3(layers, size["width"], size["heads"], size["top"] * size["ff"] + size["shared_ff"]),
+               num_key_value_heads=size["kv_heads"], head_dim=size["dim"], vocab_size=COMPARE_VOCAB)
+    return Qwen3Config.from_dict(raw)
+
+
+def gefarax_step_cost(size: dict, layers: int, tokens: int, cached_tokens: float, pairs: float):
+    """(bytes, FLOPs) of one step of ``tokens`` new tokens: bytes = every weight the step touches once (of the routed
+    experts the expected number of distinct ones its tokens choose) + ``cached_tokens`` keys and values;
+    FLOPs = the products of its tokens + attention over ``pairs`` (query, key) pairs + logits of one row per sequence
+    (left out: they are the same in both models)."""
+    width, heads, kv_heads, dim, vdim = size["width"], size["heads"], size["kv_heads"], size["dim"], size["vdim"]
+    experts, top, ff, shared_ff = size["experts"], size["top"], size["ff"], size["shared_ff"]
+    attention_weights = (heads * dim + kv_heads * dim + kv_heads * vdim) * width + width * heads * vdim
+    distinct = experts * (1.0 - (1.0 - top / experts) ** tokens)
+    weight_bytes = 2 * layers * (attention_weights + 3 * width * (distinct * ff + shared_ff)) + 4 * layers * experts * width
+    cache_bytes = 2 * layers * kv_heads * (dim + vdim) * cached_tokens
+    linear = 2 * tokens * layers * (attention_weights + 3 * width * (top * ff + shared_ff) + experts * width)
+    attention = 2 * layers * heads * (dim + vdim) * pairs
+    return weight_bytes + cache_bytes + COMPARE_VOCAB * width * 2, linear + attention
+
+
+def dense_step_cost(size: dict, layers: int, tokens: int, cached_tokens: float, pairs: float):
+    width, heads, kv_heads, dim = size["width"], size["heads"], size["kv_heads"], size["dim"]
+    inter = size["top"] * size["ff"] + size["shared_ff"]
+    weights = (heads + 2 * kv_heads) * dim * width + width * heads * dim + 3 * width * inter
+    return (2 * layers * weights + 2 * layers * kv_heads * 2 * dim * cached_tokens + COMPARE_VOCAB * width * 2,
+            2 * tokens * layers * weights + 2 * layers * heads * 2 * dim * pairs)

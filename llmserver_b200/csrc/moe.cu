@@ -2,7 +2,8 @@
 //
 //   route      z = W_r x (32-bit), s = sigmoid(z); the `top` experts with the largest s + correction are chosen
 //              (ties: the lower index), each with the weight s * scale (the correction only chooses; nothing is
-//              renormalised).  One block per token.
+//              renormalised).  One block per token.  `select` is the same choice from logits that a matrix product
+//              has already made (one warp per token).
 //   indexed    out[p] = W[index[p]] in[p / in_div]: every (token, chosen expert) pair p multiplies its own expert's
 //   linear     matrix.  One warp per output element, its sum taken over k in an order that depends on the inner size
 //              alone, so a pair's result does not depend on what else the step holds.  As a gated form the matrix
@@ -72,6 +73,52 @@ __global__ void moe_route_kernel(const T* __restrict__ x, const float* __restric
     }
 }
 
+// The choice alone, from router logits that a matrix product has made: z float32 [N, experts].  One warp per token.
+__global__ void moe_select_kernel(const float* __restrict__ logits, const float* __restrict__ correction, int* __restrict__ chosen,
+                                  float* __restrict__ weights, int n_tokens, int experts, int top, float scale) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float select_shared[];      // per warp: [experts] scores, [experts] choice scores
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int token = blockIdx.x * warps + warp;
+    if (token >= n_tokens) return;
+    float* score = select_shared + (size_t)warp * 2 * experts;
+    float* choice = score + experts;
+    for (int e = lane; e < experts; e += 32) {
+        const float s = 1.0f / (1.0f + expf(-logits[(size_t)token * experts + e]));
+        score[e] = s;
+        choice[e] = s + (correction ? correction[e] : 0.0f);
+    }
+    __syncwarp();
+    for (int j = 0; j < top; ++j) {
+        float best = -INFINITY;
+        int best_index = 0x7fffffff;
+        for (int e = lane; e < experts; e += 32) {
+            const float c = choice[e];
+            if (c > best) {
+                best = c;
+                best_index = e;
+            }
+        }
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+            const int other_index = __shfl_xor_sync(0xffffffffu, best_index, offset);
+            if (other > best || (other == best && other_index < best_index)) {
+                best = other;
+                best_index = other_index;
+            }
+        }
+        if (best_index == 0x7fffffff) best_index = 0;
+        if (lane == 0) {
+            chosen[(size_t)token * top + j] = best_index;
+            weights[(size_t)token * top + j] = score[best_index] * scale;
+            choice[best_index] = -INFINITY;
+        }
+        __syncwarp();
+    }
+}
+
 __device__ __forceinline__ float gated_activation(float gate, float up, float limit, float alpha) {
     const float g = fminf(gate, limit);
     const float u = fminf(fmaxf(up, -limit), limit);
@@ -95,9 +142,22 @@ __global__ void indexed_linear_kernel(const T* __restrict__ in, const T* __restr
     for (int r = first + warp; r < min(first + warps * 4, rows); r += warps) {
         const T* w = matrix + (size_t)r * inner;
         float sum = 0.0f, sum_up = 0.0f;
-        for (int i = lane; i < inner; i += 32) {
-            sum = fmaf(in_row[i], Num<T>::load(w + i), sum);
-            if (GATED) sum_up = fmaf(in_row[i], Num<T>::load(w + (size_t)rows * inner + i), sum_up);
+        if (inner % 8 == 0 && aligned16(weight)) {      // 16- or 32-byte runs per lane; the order depends on the inner size only
+            for (int i = lane * 8; i < inner; i += 256) {
+                float values[8], up_values[8];
+                load8<T>(w + i, values);
+                if (GATED) load8<T>(w + (size_t)rows * inner + i, up_values);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    sum = fmaf(in_row[i + j], values[j], sum);
+                    if (GATED) sum_up = fmaf(in_row[i + j], up_values[j], sum_up);
+                }
+            }
+        } else {
+            for (int i = lane; i < inner; i += 32) {
+                sum = fmaf(in_row[i], Num<T>::load(w + i), sum);
+                if (GATED) sum_up = fmaf(in_row[i], Num<T>::load(w + (size_t)rows * inner + i), sum_up);
+            }
         }
         sum = warp_sum(sum);
         if (GATED) sum_up = warp_sum(sum_up);
@@ -160,6 +220,24 @@ LLM_EXPORT int llm_moe_route(const void* x, const float* router, const float* co
                    counts, width, experts, top, scale);
     });
     return llm_check_launch("moe_route");
+}
+
+LLM_EXPORT int llm_moe_select(const float* logits, const float* correction, int* chosen, float* weights, int n_tokens,
+                              int experts, int top, float scale, cudaStream_t stream) {
+    if (n_tokens == 0) return LLM_OK;
+    if (top <= 0 || top > experts || top > MOE_MAX_TOP) {
+        llm_set_error("moe_select: top %d must lie in 1..min(%d experts, %d)", top, experts, MOE_MAX_TOP);
+        return LLM_REFUSED;
+    }
+    const int warps = 4;
+    const size_t shared = (size_t)warps * 2 * experts * sizeof(float);
+    if (shared > 40 * 1024) {
+        llm_set_error("moe_select: %d experts are too many", experts);
+        return LLM_REFUSED;
+    }
+    llm_launch(moe_select_kernel, (n_tokens + warps - 1) / warps, warps * 32, shared, stream, logits, correction, chosen, weights,
+               n_tokens, experts, top, scale);
+    return llm_check_launch("moe_select");
 }
 
 LLM_EXPORT int llm_indexed_linear(const void* in, const void* weight, const int* index, void* out, int n_pairs, int rows,

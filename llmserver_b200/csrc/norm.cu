@@ -202,6 +202,79 @@ __global__ void normed_add_rmsnorm_kernel(float* __restrict__ residual, const T*
         Num<T>::store(dst + i, updated[i] * inverse * Num<W>::load(weight + i));
 }
 
+// The same with 16-byte accesses and the row held in registers between the passes (widths that are a multiple of 8,
+// up to blockDim * 32); the order of each sum depends on the width only.
+template <typename T, typename W>
+__global__ void normed_add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                              const W* __restrict__ post_weight, float post_eps, const float* __restrict__ extra,
+                                              const W* __restrict__ weight, T* __restrict__ out, const int* __restrict__ rows,
+                                              int width, float eps, int write_residual) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int o = blockIdx.x;
+    const int r = rows ? rows[o] : o;
+    float* res = residual + (size_t)r * width;
+    const int chunks = width / kChunk;
+    float values[kMaxChunks][kChunk];
+    float inverse_post = 0.0f;
+    if (delta) {
+        const T* del = delta + (size_t)r * width;
+        float sum_squares = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kMaxChunks; ++i) {
+            const int c = threadIdx.x + i * blockDim.x;
+            if (c < chunks) {
+                load8<T>(del + c * kChunk, values[i]);
+#pragma unroll
+                for (int j = 0; j < kChunk; ++j) sum_squares += values[i][j] * values[i][j];
+            }
+        }
+        inverse_post = rsqrtf(block_sum(sum_squares, scratch) / (float)width + post_eps);
+    }
+    float sum_squares = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kMaxChunks; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < chunks) {
+            float stream[kChunk];
+            load8<float>(res + c * kChunk, stream);
+            if (delta) {
+                float scale[kChunk];
+                load8<W>(post_weight + c * kChunk, scale);
+#pragma unroll
+                for (int j = 0; j < kChunk; ++j) stream[j] += values[i][j] * inverse_post * scale[j];
+            }
+            if (extra) {
+                float more[kChunk];
+                load8<float>(extra + (size_t)r * width + c * kChunk, more);
+#pragma unroll
+                for (int j = 0; j < kChunk; ++j) stream[j] += more[j];
+            }
+            if (write_residual && (delta || extra)) store8<float>(res + c * kChunk, stream);
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) {
+                values[i][j] = stream[j];
+                sum_squares += stream[j] * stream[j];
+            }
+        }
+    }
+    if (!out) return;
+    const float inverse = rsqrtf(block_sum(sum_squares, scratch) / (float)width + eps);
+    T* dst = out + (size_t)o * width;
+#pragma unroll
+    for (int i = 0; i < kMaxChunks; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < chunks) {
+            float scale[kChunk], scaled[kChunk];
+            load8<W>(weight + c * kChunk, scale);
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) scaled[j] = values[i][j] * inverse * scale[j];
+            store8<T>(dst + c * kChunk, scaled);
+        }
+    }
+}
+
 LLM_EXPORT int llm_normed_add_rmsnorm(float* residual, const void* delta, const void* post_weight, float post_eps,
                                       const float* extra, const void* weight, void* out, const int* rows, int n_rows,
                                       int width, float eps, int write_residual, int dtype, int weight_dtype,
@@ -214,6 +287,18 @@ LLM_EXPORT int llm_normed_add_rmsnorm(float* residual, const void* delta, const 
     if (out && !weight) {
         llm_set_error("normed_add_rmsnorm: an output needs the weight of its norm");
         return LLM_REFUSED;
+    }
+    const int chunks = width / kChunk;
+    int threads = ((chunks + 31) / 32) * 32;      // depends on the width only
+    if (threads > 512) threads = 512;
+    const bool vector_form = width % kChunk == 0 && width >= kChunk && chunks <= threads * kMaxChunks && aligned16(residual) &&
+                             aligned16(delta) && aligned16(post_weight) && aligned16(extra) && aligned16(weight) && aligned16(out);
+    if (vector_form) {
+        LLM_DISPATCH_DTYPE_WEIGHT(dtype, weight_dtype,
+                                  (llm_launch(normed_add_rmsnorm_vec_kernel<T, W>, n_rows, threads, 0, stream, residual,
+                                      (const T*)delta, (const W*)post_weight, post_eps, extra, (const W*)weight, (T*)out, rows,
+                                      width, eps, write_residual)));
+        return llm_check_launch("normed_add_rmsnorm");
     }
     const size_t shared = (size_t)width * sizeof(float);
     if (shared > 200 * 1024) {

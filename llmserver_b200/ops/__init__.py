@@ -16,8 +16,9 @@ from .library import (KernelError, call, check, declare, dtype_code, launch_coun
 from .stream import STREAM_ROWS, RowScaled, StreamSink
 
 __all__ = ["KernelError", "embedding", "add_rmsnorm", "rmsnorm", "silu_mul", "sample", "qk_norm_rope_kv_write",
-           "attention_generic", "rope_kv_write_split", "normed_add_rmsnorm", "moe_route", "indexed_linear", "moe_combine",
-           "clamped_glu", "gemm_f32", "linear", "qkv_projection", "gate_up_silu", "interleave_gate_up", "require_device", "library", "launch_count",
+           "attention_generic", "rope_kv_write_split", "normed_add_rmsnorm", "moe_route", "moe_select", "indexed_linear", "moe_combine", "moe_plan", "moe_grouped",
+           "moe_grouped_supported", "moe_combine_rows", "ExpertPlan",
+           "clamped_glu", "gemm_f32", "linear", "linear_wide", "qkv_projection", "gate_up_silu", "interleave_gate_up", "require_device", "library", "launch_count",
            "RowScaled", "StreamSink", "STREAM_ROWS", "unscaled_rows_supported"]
 
 
@@ -314,6 +315,19 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, correction: Optional[torch.
     return chosen, weights
 
 
+def moe_select(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, scale: float):
+    """``moe_route``'s choice from router logits that a product has already made: logits float32 [N, E]."""
+    check(logits, "router logits", torch.float32)
+    tokens, experts = logits.shape
+    if correction is not None:
+        check(correction, "router correction", torch.float32, experts)
+    chosen = torch.empty((tokens, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((tokens, top), dtype=torch.float32, device=logits.device)
+    call("llm_moe_select", logits.data_ptr(), pointer(correction), chosen.data_ptr(), weights.data_ptr(), tokens, experts,
+         int(top), float(scale), stream_handle())
+    return chosen, weights
+
+
 def indexed_linear(x: torch.Tensor, weight: torch.Tensor, index: Optional[torch.Tensor], pairs: int, in_div: int = 1,
                    gated: Optional[tuple] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """out[p] = weight[index[p]] x[p // in_div] for p < ``pairs``; ``weight`` is [E, R, K] (``index`` None: E = 1).
@@ -356,6 +370,71 @@ def moe_combine(down: torch.Tensor, weights: torch.Tensor, shared_out: Optional[
     out = torch.empty((tokens, width), dtype=act_dtype, device=down.device)
     call("llm_moe_combine", down.data_ptr(), weights.data_ptr(), pointer(shared_out), out.data_ptr(), tokens, width, top,
          dtype_code(act_dtype), stream_handle())
+    return out
+
+
+class ExpertPlan:
+    """The (token, expert) pairs of a step sorted by expert: ``pair_of_row[r]`` is the pair that row r of the sorted
+    order holds, ``row_of_pair`` the inverse, ``offsets[e]`` the first row of expert e, ``tiles`` the row tiles the
+    grouped product walks (count first, then (expert, first row, rows) per tile)."""
+
+    def __init__(self, pairs, offsets, pair_of_row, row_of_pair, tiles, max_tiles):
+        self.pairs, self.offsets, self.pair_of_row, self.row_of_pair = pairs, offsets, pair_of_row, row_of_pair
+        self.tiles, self.max_tiles = tiles, max_tiles
+
+
+MOE_TILE_ROWS = 128
+
+
+def moe_plan(chosen: torch.Tensor, experts: int) -> ExpertPlan:
+    """Sorts the pairs of ``chosen`` (int32 [N, top]) by expert on the device; nothing comes back to the host."""
+    check(chosen, "chosen experts", torch.int32)
+    pairs = chosen.numel()
+    max_tiles = -(-pairs // MOE_TILE_ROWS) + experts
+    offsets = torch.empty((experts + 1,), dtype=torch.int32, device=chosen.device)
+    pair_of_row = torch.empty((pairs,), dtype=torch.int32, device=chosen.device)
+    row_of_pair = torch.empty((pairs,), dtype=torch.int32, device=chosen.device)
+    tiles = torch.empty((1 + 3 * max_tiles,), dtype=torch.int32, device=chosen.device)
+    call("llm_moe_plan", chosen.data_ptr(), pairs, experts, offsets.data_ptr(), pair_of_row.data_ptr(), row_of_pair.data_ptr(),
+         tiles.data_ptr(), max_tiles, stream_handle())
+    return ExpertPlan(pairs, offsets, pair_of_row, row_of_pair, tiles, max_tiles)
+
+
+def moe_grouped_supported(weight: torch.Tensor, gated: bool) -> bool:
+    """Whether the tiled product over sorted pairs takes these expert matrices ([E, rows, inner], bfloat16)."""
+    rows = weight.shape[1] // 2 if gated else weight.shape[1]
+    return weight.dtype == torch.bfloat16 and bool(library().llm_moe_grouped_supports(rows, weight.shape[2], int(gated)))
+
+
+def moe_grouped(x: torch.Tensor, weight: torch.Tensor, plan: ExpertPlan, gather_div: Optional[int] = None,
+                gated: Optional[tuple] = None) -> torch.Tensor:
+    """One tiled product over all experts: row r of the plan's order gets weight[its expert] times its input row,
+    which is x[pair_of_row[r] // gather_div] or, with ``gather_div`` None, x[r].  ``gated`` = (limit, alpha): the
+    matrices are [E, 2 R, K], gate rows first, and the result is the experts' activation in bfloat16 [pairs, R];
+    otherwise the 32-bit sums [pairs, R]."""
+    check(x, "x", torch.bfloat16)
+    check(weight, "expert weights", torch.bfloat16, x.shape[-1])
+    rows = weight.shape[1] // 2 if gated else weight.shape[1]
+    out = torch.empty((plan.pairs, rows), dtype=torch.bfloat16 if gated else torch.float32, device=x.device)
+    limit, alpha = gated if gated else (0.0, 0.0)
+    call("llm_moe_grouped", x.data_ptr(), weight.data_ptr(), plan.tiles.data_ptr(),
+         plan.pair_of_row.data_ptr() if gather_div is not None else 0, int(gather_div or 1), out.data_ptr(), rows,
+         x.shape[-1], plan.max_tiles, int(bool(gated)), float(limit), float(alpha), stream_handle())
+    return out
+
+
+def moe_combine_rows(down: torch.Tensor, plan: ExpertPlan, weights: torch.Tensor, shared_out: Optional[torch.Tensor],
+                     act_dtype: torch.dtype) -> torch.Tensor:
+    """out[t] = sum_j weights[t, j] * down[row_of_pair[t * top + j]] (+ shared_out[t]); ``down`` float32 in the plan's order."""
+    check(down, "expert outputs", torch.float32)
+    check(weights, "routing weights", torch.float32)
+    tokens, top = weights.shape
+    width = down.shape[-1]
+    if shared_out is not None:
+        check(shared_out, "shared expert output", act_dtype, width)
+    out = torch.empty((tokens, width), dtype=act_dtype, device=down.device)
+    call("llm_moe_combine_rows", down.data_ptr(), plan.row_of_pair.data_ptr(), weights.data_ptr(), pointer(shared_out),
+         out.data_ptr(), tokens, width, top, dtype_code(act_dtype), stream_handle())
     return out
 
 
@@ -404,6 +483,18 @@ def linear(x, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
     if sink is not None and out is None and not isinstance(x, RowScaled) and gemm_bf16.linear_into_stream(x, weight, sink):
         return None
     return gemm_bf16.linear_bf16(x, weight, out=out, out_dtype=out_dtype)
+
+
+def linear_wide(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """x W^T with bfloat16 operands and a float32 result taken straight from the 32-bit sums (never a rounded result
+    widened): a product with few output columns whose values decide something, a router's logits for instance.  Up
+    to 64 rows: this package's kernel; more: the library's product with a 32-bit result in one launch."""
+    if x.dtype == torch.float32:
+        return gemm_f32(x, weight)
+    from . import gemm_bf16
+    if x.shape[0] <= gemm_bf16.SMALL_M:
+        return gemm_bf16.linear_bf16(x, weight, out_dtype=torch.float32)
+    return gemm_bf16._float32_by_library(x, weight, None)
 
 
 def unscaled_rows_supported(weight: torch.Tensor) -> bool:

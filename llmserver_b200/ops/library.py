@@ -27,9 +27,14 @@ SIGNATURES = {
     "llm_rope_kv_write_split": [_P, _P, _F, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _I, _S],
     "llm_normed_add_rmsnorm": [_P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I, _S],
     "llm_moe_route": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _S],
+    "llm_moe_select": [_P, _P, _P, _P, _I, _I, _I, _F, _S],
     "llm_indexed_linear": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _S],
     "llm_moe_combine": [_P, _P, _P, _P, _I, _I, _I, _I, _S],
     "llm_clamped_glu": [_P, _P, _I, _I, _F, _F, _I, _S],
+    "llm_moe_plan": [_P, _I, _I, _P, _P, _P, _P, _I, _S],
+    "llm_moe_grouped_supports": [_I, _I, _I],
+    "llm_moe_grouped": [_P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _F, _S],
+    "llm_moe_combine_rows": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _S],
     "llm_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _S],
     "llm_attention_mma_supports": [_I, _I, _I],
     "llm_attention_mma_sinks_supports": [_I, _I, _I, _I],

@@ -64,6 +64,11 @@ class RoutedExperts(FeedForward):
                                     for e in range(self.experts)]).contiguous()
         self.down = torch.stack([weights[f"e{e}.down"] for e in range(self.experts)]).contiguous()
         self.router = weights["router"].to(torch.float32).contiguous()
+        # A router whose weights are bfloat16 numbers (what a bfloat16 checkpoint holds) can be multiplied on the tensor
+        # cores without leaving 32-bit arithmetic: products of two bfloat16 numbers are exact in 32-bit, and the sums
+        # are 32-bit.  Any other router, and the 32-bit path, use the FMA kernel that makes the choice as well.
+        narrow = self.router.to(torch.bfloat16)
+        self.router_narrow = narrow.contiguous() if runtime.dtype == torch.bfloat16 and bool((narrow.float() == self.router).all()) else None
         self.correction = weights["correction"].to(torch.float32).contiguous() if params.get("correction", True) else None
         self.shared_gate_up = self.shared_down = None
         if params.get("shared_intermediate"):
@@ -71,15 +76,31 @@ class RoutedExperts(FeedForward):
             self.shared_down = weights["shared.down"].contiguous()
             self.shared_limit = float(params.get("shared_limit", self.limit))
 
+        # bfloat16 steps of more than a few tokens sort their (token, expert) pairs by expert and run one tiled product
+        # over all experts; the 32-bit path and steps of few tokens multiply pair by pair, reading each pair's matrices
+        self.grouped = (runtime.dtype == torch.bfloat16 and ops.moe_grouped_supported(self.gate_up, True)
+                        and ops.moe_grouped_supported(self.down, False) and self.down.shape[1] % 4 == 0)
+
+    GROUPED_FROM = 16     # tokens from which pairs are sorted and multiplied tile by tile
+
     def forward(self, x):
         tokens = x.shape[0]
-        chosen, weights = ops.moe_route(x, self.router, self.correction, self.top, self.route_scale)
-        pairs = tokens * self.top
-        index = chosen.view(-1)
-        hidden = ops.indexed_linear(x, self.gate_up, index, pairs, in_div=self.top, gated=(self.limit, self.alpha))
-        down = ops.indexed_linear(hidden, self.down, index, pairs, out_dtype=torch.float32)
+        if self.router_narrow is not None:
+            logits = ops.linear_wide(x, self.router_narrow)
+            chosen, weights = ops.moe_select(logits, self.correction, self.top, self.route_scale)
+        else:
+            chosen, weights = ops.moe_route(x, self.router, self.correction, self.top, self.route_scale)
         shared = None
         if self.shared_gate_up is not None:
             shared = ops.linear(ops.clamped_glu(ops.linear(x, self.shared_gate_up), self.shared_limit, self.alpha),
                                 self.shared_down)
+        if self.grouped and tokens >= self.GROUPED_FROM:
+            plan = ops.moe_plan(chosen, self.experts)
+            hidden = ops.moe_grouped(x, self.gate_up, plan, gather_div=self.top, gated=(self.limit, self.alpha))
+            down = ops.moe_grouped(hidden, self.down, plan)
+            return ops.moe_combine_rows(down, plan, weights, shared, self.runtime.dtype)
+        pairs = tokens * self.top
+        index = chosen.view(-1)
+        hidden = ops.indexed_linear(x, self.gate_up, index, pairs, in_div=self.top, gated=(self.limit, self.alpha))
+        down = ops.indexed_linear(hidden, self.down, index, pairs, out_dtype=torch.float32)
         return ops.moe_combine(down, weights, shared, self.runtime.dtype)

@@ -314,8 +314,13 @@ def test_router(dtype, experts, top, width):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("experts,top,width,inter,shared", [(4, 2, 64, 48, 32), (5, 1, 48, 24, None), (3, 3, 96, 40, 56)])
-def test_routed_experts_part(dtype, experts, top, width, inter, shared):
+@pytest.mark.parametrize("experts,top,width,inter,shared,tokens", [
+    (4, 2, 64, 48, 32, 37), (5, 1, 48, 24, None, 37), (3, 3, 96, 40, 56, 37),
+    # sizes the tiled product over sorted pairs takes (bfloat16, 16 tokens or more): experts with several row tiles, with
+    # a handful of rows and with none, feature counts that fill a column tile and that do not; and the same sizes with
+    # so few tokens that each pair multiplies alone
+    (3, 2, 128, 64, 64, 400), (9, 3, 192, 136, None, 150), (6, 2, 128, 64, 64, 5), (40, 4, 64, 72, 8, 33)])
+def test_routed_experts_part(dtype, experts, top, width, inter, shared, tokens):
     from llmserver_b200.parts import FEED_FORWARDS, Runtime
     generator = torch.Generator().manual_seed(experts + width)
     params = dict(hidden=width, experts=experts, top=top, intermediate=inter, limit=0.9, route_scale=1.3)
@@ -331,14 +336,14 @@ def test_routed_experts_part(dtype, experts, top, width, inter, shared):
     torch_dtype = getattr(torch, dtype)
     part = cls(params, {name: (value.float() if name in ("router", "correction") else value.to(torch_dtype)).to(DEVICE)
                         for name, value in raw.items()}, Runtime(torch_dtype, torch.device(DEVICE)))
-    x = torch.randn((37, width), generator=generator).to(torch_dtype)
+    x = torch.randn((tokens, width), generator=generator).to(torch_dtype)
     want_weights = {"m." + name: value.double() for name, value in raw.items()}
     margins = []
     want = plain.moe(x.double(), mlp, want_weights, "m.", margins)
     got = part.forward(x.to(DEVICE)).cpu().double()
     rows = margins[0] > (1e-4 if dtype == "float32" else 1e-2)
     tolerance = 2e-5 if dtype == "float32" else 2e-2
-    assert rows.sum() > 20
+    assert rows.sum() > tokens // 2
     assert torch.allclose(got[rows], want[rows], atol=tolerance * float(want.abs().max()), rtol=tolerance)
     # the clamps were exercised: some gate or up value lay beyond the limit
     gate = x.double() @ want_weights["m.e0.gate"].T
@@ -346,7 +351,7 @@ def test_routed_experts_part(dtype, experts, top, width, inter, shared):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("width", [48, 64, 1000])
+@pytest.mark.parametrize("width", [48, 50, 64, 1000, 4100])
 def test_normed_delta_joins_the_stream(dtype, width):
     from llmserver_b200 import ops
     generator = torch.Generator().manual_seed(width)
