@@ -7,6 +7,7 @@ The residual stream is always float32; "activation type" is the model's dtype (f
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -400,10 +401,17 @@ def moe_plan(chosen: torch.Tensor, experts: int) -> ExpertPlan:
     return ExpertPlan(pairs, offsets, pair_of_row, row_of_pair, tiles, max_tiles)
 
 
+# "tcgen05" (default): the tiled product with its accumulator in tensor memory; "mma": the mma.sync kernel
+MOE_GROUPED_KERNEL = os.environ.get("LLMSERVER_B200_MOE_GROUPED", "tcgen05")
+
+
 def moe_grouped_supported(weight: torch.Tensor, gated: bool) -> bool:
-    """Whether the tiled product over sorted pairs takes these expert matrices ([E, rows, inner], bfloat16)."""
+    """Whether a tiled product over sorted pairs takes these expert matrices ([E, rows, inner], bfloat16)."""
     rows = weight.shape[1] // 2 if gated else weight.shape[1]
-    return weight.dtype == torch.bfloat16 and bool(library().llm_moe_grouped_supports(rows, weight.shape[2], int(gated)))
+    if weight.dtype != torch.bfloat16:
+        return False
+    return bool(library().llm_moe_grouped_tc_supports(rows, weight.shape[2], int(gated))) or \
+        bool(library().llm_moe_grouped_supports(rows, weight.shape[2], int(gated)))
 
 
 def moe_grouped(x: torch.Tensor, weight: torch.Tensor, plan: ExpertPlan, gather_div: Optional[int] = None,
@@ -411,15 +419,27 @@ def moe_grouped(x: torch.Tensor, weight: torch.Tensor, plan: ExpertPlan, gather_
     """One tiled product over all experts: row r of the plan's order gets weight[its expert] times its input row,
     which is x[pair_of_row[r] // gather_div] or, with ``gather_div`` None, x[r].  ``gated`` = (limit, alpha): the
     matrices are [E, 2 R, K], gate rows first, and the result is the experts' activation in bfloat16 [pairs, R];
-    otherwise the 32-bit sums [pairs, R]."""
+    otherwise the 32-bit sums [pairs, R].  On tcgen05 where that kernel takes the sizes (it reads its rows by TMA, so
+    rows that have to be gathered are copied into the plan's order first), else the mma.sync kernel."""
     check(x, "x", torch.bfloat16)
     check(weight, "expert weights", torch.bfloat16, x.shape[-1])
     rows = weight.shape[1] // 2 if gated else weight.shape[1]
+    inner = x.shape[-1]
     out = torch.empty((plan.pairs, rows), dtype=torch.bfloat16 if gated else torch.float32, device=x.device)
     limit, alpha = gated if gated else (0.0, 0.0)
+    if MOE_GROUPED_KERNEL != "mma" and library().llm_moe_grouped_tc_supports(rows, inner, int(bool(gated))) and (gated or rows % 4 == 0):
+        if gather_div is not None:
+            ordered = torch.empty((plan.pairs, inner), dtype=torch.bfloat16, device=x.device)
+            call("llm_moe_gather_rows", x.data_ptr(), plan.pair_of_row.data_ptr(), int(gather_div), ordered.data_ptr(), plan.pairs,
+                 inner, stream_handle())
+            x = ordered
+        call("llm_moe_grouped_tc", x.data_ptr(), plan.pairs, weight.data_ptr(), weight.shape[0], plan.tiles.data_ptr(), out.data_ptr(),
+             rows, inner, plan.max_tiles, int(bool(gated)), float(limit), float(alpha), wait_error_flag(x.device).data_ptr(),
+             stream_handle())
+        return out
     call("llm_moe_grouped", x.data_ptr(), weight.data_ptr(), plan.tiles.data_ptr(),
          plan.pair_of_row.data_ptr() if gather_div is not None else 0, int(gather_div or 1), out.data_ptr(), rows,
-         x.shape[-1], plan.max_tiles, int(bool(gated)), float(limit), float(alpha), stream_handle())
+         inner, plan.max_tiles, int(bool(gated)), float(limit), float(alpha), stream_handle())
     return out
 
 

@@ -34,6 +34,9 @@ SIGNATURES = {
     "llm_moe_plan": [_P, _I, _I, _P, _P, _P, _P, _I, _S],
     "llm_moe_grouped_supports": [_I, _I, _I],
     "llm_moe_grouped": [_P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _F, _S],
+    "llm_moe_grouped_tc_supports": [_I, _I, _I],
+    "llm_moe_gather_rows": [_P, _P, _I, _P, _I, _I, _S],
+    "llm_moe_grouped_tc": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _F, _F, _P, _S],
     "llm_moe_combine_rows": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _S],
     "llm_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _S],
     "llm_attention_mma_supports": [_I, _I, _I],
@@ -179,5 +182,5 @@ def check_wait_errors() -> None:
             flag.zero_()
             raise KernelError(f"a kernel gave up waiting on one of its barriers (code {code}: 2 matrix product, "
                               "3 decode attention, 4 prompt attention), or attention met a block-table entry that names no "
-                              "page of the pool (5) or a context that needs more splits than it was given (6); the step's "
-                              "result is invalid")
+                              "page of the pool (5) or a context that needs more splits than it was given (6), or the experts' "
+                              "tiled product gave up waiting (7); the step's result is invalid")

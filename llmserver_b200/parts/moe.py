@@ -79,7 +79,8 @@ class RoutedExperts(FeedForward):
         # bfloat16 steps of more than a few tokens sort their (token, expert) pairs by expert and run one tiled product
         # over all experts; the 32-bit path and steps of few tokens multiply pair by pair, reading each pair's matrices
         self.grouped = (runtime.dtype == torch.bfloat16 and ops.moe_grouped_supported(self.gate_up, True)
-                        and ops.moe_grouped_supported(self.down, False) and self.down.shape[1] % 4 == 0)
+                        and ops.moe_grouped_supported(self.down, False) and self.down.shape[1] % 4 == 0
+                        and self.gate_up.shape[2] % 64 == 0 and self.down.shape[2] % 64 == 0)
 
     GROUPED_FROM = 16     # tokens from which pairs are sorted and multiplied tile by tile
 

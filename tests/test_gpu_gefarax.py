@@ -319,9 +319,15 @@ def test_router(dtype, experts, top, width):
     # sizes the tiled product over sorted pairs takes (bfloat16, 16 tokens or more): experts with several row tiles, with
     # a handful of rows and with none, feature counts that fill a column tile and that do not; and the same sizes with
     # so few tokens that each pair multiplies alone
-    (3, 2, 128, 64, 64, 400), (9, 3, 192, 136, None, 150), (6, 2, 128, 64, 64, 5), (40, 4, 64, 72, 8, 33)])
-def test_routed_experts_part(dtype, experts, top, width, inter, shared, tokens):
+    (3, 2, 128, 64, 64, 400), (5, 2, 128, 192, 64, 300), (7, 3, 320, 448, None, 260), (9, 3, 192, 136, None, 150),
+    (6, 2, 128, 64, 64, 5), (40, 4, 64, 72, 8, 33)])
+@pytest.mark.parametrize("kernel", ["tcgen05", "mma"])
+def test_routed_experts_part(dtype, experts, top, width, inter, shared, tokens, kernel):
+    from llmserver_b200 import ops
+    from llmserver_b200.ops.library import check_wait_errors
     from llmserver_b200.parts import FEED_FORWARDS, Runtime
+    if kernel == "mma" and (dtype == "float32" or tokens < 16 or width % 64 or inter % 64):
+        pytest.skip("the choice of tiled kernel only matters where one runs")
     generator = torch.Generator().manual_seed(experts + width)
     params = dict(hidden=width, experts=experts, top=top, intermediate=inter, limit=0.9, route_scale=1.3)
     mlp = {"router": {"experts": experts, "top": top, "scale": 1.3}, "expert": {"ff": inter, "limit": 0.9}, "shared": None}
@@ -340,7 +346,12 @@ def test_routed_experts_part(dtype, experts, top, width, inter, shared, tokens):
     want_weights = {"m." + name: value.double() for name, value in raw.items()}
     margins = []
     want = plain.moe(x.double(), mlp, want_weights, "m.", margins)
-    got = part.forward(x.to(DEVICE)).cpu().double()
+    before, ops.MOE_GROUPED_KERNEL = ops.MOE_GROUPED_KERNEL, kernel
+    try:
+        got = part.forward(x.to(DEVICE)).cpu().double()
+    finally:
+        ops.MOE_GROUPED_KERNEL = before
+    check_wait_errors()
     rows = margins[0] > (1e-4 if dtype == "float32" else 1e-2)
     tolerance = 2e-5 if dtype == "float32" else 2e-2
     assert rows.sum() > tokens // 2
@@ -530,3 +541,21 @@ def test_trace_run_program(folders, tmp_path):
         if wanted:
             got[record["step"]] = np.fromfile(out_dir / f"{record['step']}.f32", dtype="<f4").reshape(wanted, vocab)
     compare(got, records, requests, folders[name], dtype, f"trace_run {name}")
+
+
+def test_generate_command(folders):
+    """The command line a user generates with: ids in, ids out, the model chosen by its config.json."""
+    name = "no_loop"
+    vocab = GEFARAX[name][0]["vocab"]
+    prompts = [tokens_for(vocab, 19, 71), tokens_for(vocab, 3, 72)]
+    command = [sys.executable, "-m", "llmserver_b200.cli.generate", "--model", folders[name], "--dtype", "float32",
+               "--max-new-tokens", "6", "--ignore-eos", "--block-size", "8", "--json"]
+    for prompt in prompts:
+        command += ["--prompt-ids", ",".join(str(token) for token in prompt)]
+    process = subprocess.run(command, capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert process.returncode == 0, process.stderr[-2000:]
+    generated = json.loads(process.stdout.strip().splitlines()[-1])["generated"]
+    for prompt, tokens in zip(prompts, generated):
+        assert len(tokens) == 6
+        logits, _ = plain_logits(folders[name], list(prompt) + list(tokens))
+        assert tokens == [int(logits[len(prompt) - 1 + index].argmax()) for index in range(6)]
