@@ -73,14 +73,17 @@ def supported(head_dim: int, n_q_heads: int, n_kv_heads: int) -> bool:
     return bool(library().llm_attention_mma_supports(head_dim, n_q_heads, n_kv_heads))
 
 
-def plan(batch, group: int, n_kv_heads: int, device=None):
+def plan(batch, group: int, n_kv_heads: int, device=None, blocks_per_sm: int = DECODE_BLOCKS_PER_SM, cluster: bool = None):
     """Launch shape of a batch, derived once per step from its host-side lengths (and the number of SMs: the split
-    count fixes the order of the partial sums, so it is a function of the batch and the GPU model only)."""
-    key = ("attention_mma", group, n_kv_heads)
+    count fixes the order of the partial sums, so it is a function of the batch and the GPU model only).
+    ``blocks_per_sm``: decode blocks an SM holds at a time; ``cluster``: whether splits merge inside a cluster (which
+    bounds their number) or through the merge kernel."""
+    cluster = CLUSTER_MERGE if cluster is None else cluster
+    key = ("attention_mma", group, n_kv_heads, blocks_per_sm, cluster)
     cached = batch.scratch.get(key)
     if cached is not None:
         return cached
-    wave_blocks = DECODE_BLOCKS_PER_SM * _sm_count(device if device is not None else batch.context_len.device)
+    wave_blocks = blocks_per_sm * _sm_count(device if device is not None else batch.context_len.device)
     singles = sum(1 for length in batch.q_lens if length == 1)
     run_decode = singles > 0
     run_portions = singles < batch.n_seqs
@@ -93,8 +96,8 @@ def plan(batch, group: int, n_kv_heads: int, device=None):
         # equal splits beat ragged ones, and one wave beats one and a half.
         pairs = singles * n_kv_heads
         splits = max(1, min(wave_blocks // pairs, -(-longest // MIN_SPLIT)))
-        if CLUSTER_MERGE:
-            lone_blocks = pairs * WIDE_CLUSTER_SPLITS <= wave_blocks // DECODE_BLOCKS_PER_SM
+        if cluster:
+            lone_blocks = pairs * WIDE_CLUSTER_SPLITS <= wave_blocks // blocks_per_sm
             # a cluster has up to 8 blocks, or exactly 16
             splits = WIDE_CLUSTER_SPLITS if lone_blocks and splits > 12 else min(splits, MAX_CLUSTER_SPLITS)
         if pairs > wave_blocks:
@@ -183,6 +186,9 @@ def try_attention(qkv, q_stride, batch, block_tables, k_pages, v_pages, n_q_head
     return out
 
 
+PRECISE_DECODE_BLOCKS_PER_SM = int(os.environ.get("LLMSERVER_B200_PRECISE_DECODE_BLOCKS", "3"))
+
+
 def try_attention_precise(qkv, q_stride, batch, block_tables, k_pages, v_pages, n_q_heads, n_kv_heads, head_dim, value_dim,
                           scale, window, sinks):
     """The tensor-core kernels in the form that keeps attention weights at 16 significant bits through the P V product,
@@ -196,7 +202,10 @@ def try_attention_precise(qkv, q_stride, batch, block_tables, k_pages, v_pages, 
     check(block_tables, "block_tables", torch.int32)
     if sinks is not None:
         check(sinks, "sinks", torch.float32, n_q_heads)
-    run_portions, tiles, run_decode, split_len, max_splits = plan(batch, n_q_heads // n_kv_heads, n_kv_heads, qkv.device)
+    # the cp.async decode kernel keeps two tiles in flight per block: three blocks an SM (its shared memory allows them)
+    # and splits without the cluster's bound keep more bytes in flight
+    run_portions, tiles, run_decode, split_len, max_splits = plan(batch, n_q_heads // n_kv_heads, n_kv_heads, qkv.device,
+                                                                  blocks_per_sm=PRECISE_DECODE_BLOCKS_PER_SM, cluster=False)
     out = torch.empty((batch.n_tokens, n_q_heads * value_dim), dtype=torch.bfloat16, device=qkv.device)
     partial_out = partial_ml = None
     if run_decode and max_splits > 1:
