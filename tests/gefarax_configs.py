@@ -63,5 +63,23 @@ LOOP_IN_THE_MIDDLE = {
     "loop": {"start": 1, "stop": 2, "times": 3},
 }
 
+# sizes at which the bfloat16 path leaves the kernels for every size: key and value heads of 64 and 128 (tensor-core
+# attention), widths and expert sizes that are multiples of 64 (the tiled expert product for steps of 16 tokens or more)
+TENSOR_CORE_SIZES = {
+    "architecture": "Gefarax", "vocab": 211, "width": 128, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "attention",
+         "mixer": {"heads": 2, "kv_heads": 1, "dim": 64, "vdim": 128, "scale": 0.125,
+                   "rot": _rot(40000.0, 32, {"factor": 4.0, "original": 64, "fast": 16.0, "slow": 1.0})},
+         "mlp": _mlp(4, 2, 1.1, 64, 1.4, {"ff": 64, "limit": 1.8})},
+        {"type": "attention",
+         "mixer": {"heads": 4, "kv_heads": 2, "dim": 128, "vdim": 64, "scale": 0.09,
+                   "rot": _rot(10000.0, 128, {"factor": 8.0, "original": 32, "fast": 8.0, "slow": 2.0})},
+         "mlp": _mlp(3, 1, 1.6, 128, 0.7)},
+    ],
+    "loop": {"start": 1, "stop": 2, "times": 2},
+}
+
 # name -> (config.json dict, weight seed)
-GEFARAX = {"loop_from_start": (LOOP_FROM_START, 11), "no_loop": (NO_LOOP, 12), "loop_in_the_middle": (LOOP_IN_THE_MIDDLE, 13)}
+GEFARAX = {"loop_from_start": (LOOP_FROM_START, 11), "no_loop": (NO_LOOP, 12), "loop_in_the_middle": (LOOP_IN_THE_MIDDLE, 13),
+           "tensor_core_sizes": (TENSOR_CORE_SIZES, 14)}
