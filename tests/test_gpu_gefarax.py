@@ -381,6 +381,12 @@ def test_normed_delta_joins_the_stream(dtype, width):
         tolerance = 1e-5 if dtype == torch.float32 else 1e-2
         assert torch.allclose(on_device.cpu().double(), updated, atol=1e-5, rtol=1e-5)          # the stream is 32-bit in either path
         assert torch.allclose(got.cpu().double(), want, atol=tolerance, rtol=tolerance)
+        if use_extra:
+            # a second stream alone, nothing to normalise: what the model does when the block in front left a plain delta
+            on_device = stream.to(DEVICE)
+            assert ops.normed_add_rmsnorm(on_device, None, None, 0.0, None, 0.0, extra=extra.to(DEVICE), want_output=False,
+                                          act_dtype=dtype) is None
+            assert torch.allclose(on_device.cpu().double(), stream.double() + extra.double(), atol=1e-6, rtol=1e-6)
         # selected rows: the stream stays as it was
         on_device = stream.to(DEVICE)
         picked = torch.tensor([4, 0, 8], dtype=torch.int32, device=DEVICE)
