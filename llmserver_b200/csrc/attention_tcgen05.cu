@@ -68,6 +68,7 @@ struct PrefillParams {
     int skip_single;
     int pairing;
     int* error_flag;
+    const float* sinks;  // [Hq] or null: exp(sinks[h]) joins head h's softmax denominator (no key, no value, not scaled)
 };
 
 using tma::mbar_arrive;
@@ -78,6 +79,11 @@ using tma::smem_u32;
 
 using namespace tc5;
 
+// PRECISE: every probability reaches the P V product as two bfloat16 numbers, its rounding in the first 32 columns of
+// S_b and the rounding of what that left over in the other 32 (the softmax thread holds all 64 scores of its row in
+// registers by then, so S_b's own columns are free), and the P V product is two MMAs per 16 keys: 16 significant bits
+// for models whose attention weights have to stay 32-bit.
+template <bool PRECISE>
 __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                              const __grid_constant__ CUtensorMap map_k,
                                                                              const __grid_constant__ CUtensorMap map_v,
@@ -252,8 +258,13 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
                     fence_after();
 #pragma unroll
                     for (int kk = 0; kk < kKeys / 16; ++kk)     // 16 keys = 8 packed columns of P, two 8-key groups of V
+                    {
                         mma_ts(tmem + kColO, tmem + (b ? kColS1 : kColS0) + kk * 8,
                                desc_mn_major(v_smem + s * kKVBytes + kk * 4096u, 1024u, 2048u), idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
+                        if (PRECISE)
+                            mma_ts(tmem + kColO, tmem + (b ? kColS1 : kColS0) + 32 + kk * 8,
+                                   desc_mn_major(v_smem + s * kKVBytes + kk * 4096u, 1024u, 2048u), idesc_o, 1u);
+                    }
                     mma_commit(smem_u32(&v_free[s]));
                     mma_commit(smem_u32(&o_done));
                     if (t == n_tiles - 1) mma_commit(smem_u32(&o_final));
@@ -324,6 +335,14 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
             uint32_t packed[32];
 #pragma unroll
             for (int c = 0; c < 32; ++c) packed[c] = pack2(weight[2 * c], weight[2 * c + 1]);      // keys 2c, 2c + 1
+            uint32_t rest[PRECISE ? 32 : 1];
+            if (PRECISE) {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const float2 rounded = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&packed[c]));
+                    rest[c] = pack2(weight[2 * c] - rounded.x, weight[2 * c + 1] - rounded.y);
+                }
+            }
             row_sum = row_sum * factor + tile_sum;
             // O is rescaled (by the whole warp, rows that need nothing use 1) once the previous P V is done
             if (j > 0 && __any_sync(0xffffffffu, factor != 1.0f)) {
@@ -339,6 +358,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
                 }
             }
             tmem_store_32(s_address, packed);          // P over the first 32 columns of S_b
+            if (PRECISE) tmem_store_32(s_address + 32, reinterpret_cast<const uint32_t (&)[32]>(rest));
             tmem_wait_store();
             fence_before();
             __syncwarp();
@@ -350,6 +370,8 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
         if (ok && !mbar_wait(smem_u32(&o_final), 0)) ok = false;
         fence_after();
         if (!ok) failed = 1;
+        if (p.sinks != nullptr && exists && reference > -INFINITY)      // sums are relative to `reference`; so is the sink's term
+            row_sum += exp2f(p.sinks[head] * kLog2e - reference);
         const float inverse = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
         __nv_bfloat16* dst = exists ? p.out + (size_t)(token0 + token) * p.n_q_heads * kDim + (size_t)head * kDim
                                     : nullptr;
@@ -406,11 +428,11 @@ LLM_EXPORT int llm_attention_prefill_tcgen05_supports(int head_dim, int n_q_head
 
 // total_pairs: the number of CTAs: with pairing, the sum over the sequences it handles of ceil(ceil(q_len * group / 128) / 2)
 // (each CTA takes a row tile and its mirror, which evens out the work of a causal prompt); without, one CTA per tile; sequences of one token are skipped when skip_single is set (the decode kernel takes them).
-LLM_EXPORT int llm_attention_prefill_tcgen05(const void* q, int q_stride, int n_tokens, const void* k_pages, const void* v_pages,
-                                             const int* block_tables, int max_blocks, const int* q_start,
-                                             const int* context_len, void* out, int n_seqs, int n_q_heads, int n_kv_heads,
-                                             int head_dim, int page_size, int num_pages, float scale, int window, int skip_single, int pairing,
-                                             int total_pairs, int* error_flag, cudaStream_t stream) {
+static int launch_prefill_tcgen05(const void* q, int q_stride, int n_tokens, const void* k_pages, const void* v_pages,
+                                  const int* block_tables, int max_blocks, const int* q_start,
+                                  const int* context_len, void* out, int n_seqs, int n_q_heads, int n_kv_heads,
+                                  int head_dim, int page_size, int num_pages, float scale, int window, int skip_single, int pairing,
+                                  int total_pairs, int* error_flag, const float* sinks, bool precise, cudaStream_t stream) {
     if (total_pairs <= 0) return LLM_OK;
     if (num_pages <= 0) {
         llm_set_error("attention_prefill_tcgen05: the page pool has %d pages", num_pages);
@@ -455,9 +477,38 @@ LLM_EXPORT int llm_attention_prefill_tcgen05(const void* q, int q_stride, int n_
     p.skip_single = skip_single;
     p.pairing = pairing;
     p.error_flag = error_flag;
+    p.sinks = sinks;
     const size_t shared = kSharedBytes;
-    if (int limit_status = llm_raise_shared_limit(reinterpret_cast<const void*>(attention_prefill_tcgen05_kernel), shared, "attention_prefill_tcgen05", true)) return limit_status;
     dim3 grid(total_pairs, n_kv_heads);
-    llm_launch(attention_prefill_tcgen05_kernel, grid, kThreads, shared, stream, map_q, map_k, map_v, p);
+    if (precise) {
+        if (int limit_status = llm_raise_shared_limit(reinterpret_cast<const void*>(attention_prefill_tcgen05_kernel<true>), shared, "attention_prefill_tcgen05", true)) return limit_status;
+        llm_launch(attention_prefill_tcgen05_kernel<true>, grid, kThreads, shared, stream, map_q, map_k, map_v, p);
+    } else {
+        if (int limit_status = llm_raise_shared_limit(reinterpret_cast<const void*>(attention_prefill_tcgen05_kernel<false>), shared, "attention_prefill_tcgen05", true)) return limit_status;
+        llm_launch(attention_prefill_tcgen05_kernel<false>, grid, kThreads, shared, stream, map_q, map_k, map_v, p);
+    }
     return llm_check_launch("attention_prefill_tcgen05");
+}
+
+LLM_EXPORT int llm_attention_prefill_tcgen05(const void* q, int q_stride, int n_tokens, const void* k_pages, const void* v_pages,
+                                             const int* block_tables, int max_blocks, const int* q_start,
+                                             const int* context_len, void* out, int n_seqs, int n_q_heads, int n_kv_heads,
+                                             int head_dim, int page_size, int num_pages, float scale, int window, int skip_single, int pairing,
+                                             int total_pairs, int* error_flag, cudaStream_t stream) {
+    return launch_prefill_tcgen05(q, q_stride, n_tokens, k_pages, v_pages, block_tables, max_blocks, q_start, context_len, out, n_seqs,
+                                  n_q_heads, n_kv_heads, head_dim, page_size, num_pages, scale, window, skip_single, pairing,
+                                  total_pairs, error_flag, nullptr, false, stream);
+}
+
+// The same with attention weights of 16 significant bits in the P V product and, with `sinks` (float32 [Hq], may be
+// null), one more term exp(sinks[h]) in every row's softmax denominator.
+LLM_EXPORT int llm_attention_prefill_tcgen05_precise(const void* q, int q_stride, int n_tokens, const void* k_pages, const void* v_pages,
+                                                     const int* block_tables, int max_blocks, const int* q_start,
+                                                     const int* context_len, void* out, int n_seqs, int n_q_heads, int n_kv_heads,
+                                                     int head_dim, int page_size, int num_pages, float scale, int window,
+                                                     int skip_single, int pairing, int total_pairs, int* error_flag,
+                                                     const float* sinks, cudaStream_t stream) {
+    return launch_prefill_tcgen05(q, q_stride, n_tokens, k_pages, v_pages, block_tables, max_blocks, q_start, context_len, out, n_seqs,
+                                  n_q_heads, n_kv_heads, head_dim, page_size, num_pages, scale, window, skip_single, pairing,
+                                  total_pairs, error_flag, sinks, true, stream);
 }

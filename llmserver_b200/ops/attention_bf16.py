@@ -186,6 +186,8 @@ def try_attention(qkv, q_stride, batch, block_tables, k_pages, v_pages, n_q_head
     return out
 
 
+# "tcgen05" (default): prompts of heads of 128 run the tcgen05 kernel's two-part-weights form; "mma": the mma.sync kernel
+PRECISE_PREFILL_KERNEL = os.environ.get("LLMSERVER_B200_PRECISE_PREFILL", "tcgen05")
 PRECISE_DECODE_BLOCKS_PER_SM = int(os.environ.get("LLMSERVER_B200_PRECISE_DECODE_BLOCKS", "3"))
 
 
@@ -216,6 +218,26 @@ def try_attention_precise(qkv, q_stride, batch, block_tables, k_pages, v_pages, 
                        torch.empty((batch.n_tokens, n_q_heads, max_splits, 2), dtype=torch.float32, device=qkv.device))
             batch.scratch[key] = scratch
         partial_out, partial_ml = scratch
+    page_size = k_pages.shape[2]
+    if run_portions and value_dim == head_dim and PRECISE_PREFILL_KERNEL == "tcgen05" and \
+            prefill_tcgen05_supported(head_dim, n_q_heads, n_kv_heads, page_size):
+        # prompt portions on the 128-row tcgen05 kernel in its form with two-part weights; single tokens, if any, below
+        group = n_q_heads // n_kv_heads
+        tokens_per_tile = PREFILL_TILE // group
+        tile_counts = [-(-length // tokens_per_tile) for length in batch.q_lens if length > 1 or not run_decode]
+        paired = sum((count + 1) // 2 for count in tile_counts)
+        slots = _block_slots(qkv.device, False)
+        cost_paired = 2.0 * -(-paired * n_kv_heads // slots)
+        cost_single = 1.3 * max(sum(tile_counts) * n_kv_heads / slots, 1.0)
+        pairing = cost_paired < cost_single if FORCE_PAIRING is None else FORCE_PAIRING
+        call("llm_attention_prefill_tcgen05_precise", qkv.data_ptr(), q_stride, batch.n_tokens, k_pages.data_ptr(), v_pages.data_ptr(),
+             block_tables.data_ptr(), block_tables.shape[-1], batch.q_start.data_ptr(), batch.context_len.data_ptr(),
+             out.data_ptr(), batch.n_seqs, n_q_heads, n_kv_heads, head_dim, page_size, k_pages.shape[0], float(scale), int(window),
+             int(run_decode), int(pairing), paired if pairing else sum(tile_counts), wait_error_flag(qkv.device).data_ptr(),
+             0 if sinks is None else sinks.data_ptr(), stream_handle())
+        run_portions = False
+        if not run_decode:
+            return out
     call("llm_attention_mma_sinks", qkv.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(), block_tables.data_ptr(),
          block_tables.shape[-1], batch.q_start.data_ptr(), batch.context_len.data_ptr(), out.data_ptr(), batch.n_seqs,
          n_q_heads, n_kv_heads, head_dim, value_dim, k_pages.shape[2], k_pages.shape[0], float(scale), int(window),

@@ -73,7 +73,7 @@ TENSOR_CORE_SIZES = {
                    "rot": _rot(40000.0, 32, {"factor": 4.0, "original": 64, "fast": 16.0, "slow": 1.0})},
          "mlp": _mlp(4, 2, 1.1, 64, 1.4, {"ff": 64, "limit": 1.8})},
         {"type": "attention",
-         "mixer": {"heads": 4, "kv_heads": 2, "dim": 128, "vdim": 64, "scale": 0.09,
+         "mixer": {"heads": 4, "kv_heads": 2, "dim": 128, "vdim": 128, "scale": 0.09,
                    "rot": _rot(10000.0, 128, {"factor": 8.0, "original": 32, "fast": 8.0, "slow": 2.0})},
          "mlp": _mlp(3, 1, 1.6, 128, 0.7)},
     ],

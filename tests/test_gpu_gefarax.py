@@ -257,21 +257,25 @@ def test_attention_with_sinks_and_value_size(dtype, heads, kv_heads, dim, vdim):
     assert (without.cpu().double() - want).abs().max() > 0.05
 
 
-@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 64, 64), (8, 1, 128, 128), (6, 2, 64, 128), (16, 1, 128, 64), (5, 5, 64, 64)])
-def test_tensor_core_attention_with_sinks(heads, kv_heads, dim, vdim):
+@pytest.mark.parametrize("prefill", ["tcgen05", "mma"])
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 64, 64), (8, 1, 128, 128), (10, 2, 128, 128), (6, 2, 64, 128), (16, 1, 128, 64), (5, 5, 64, 64)])
+def test_tensor_core_attention_with_sinks(heads, kv_heads, dim, vdim, prefill):
     """The bfloat16 kernels a step uses for these head sizes: a whole prompt, a portion behind cached tokens, single
     decoded tokens of short contexts and of one long enough to be split, all in one batch; sinks from -2 to 3; one
     decoded query's score for a key far back towers over the rest, so weights rounded to 8 bits would not pass either
     (the row is compared to 3e-3 of its size)."""
     from llmserver_b200 import ops
     from llmserver_b200.engine.batch import SequenceSlice, build_batch
+    from llmserver_b200.ops import attention_bf16
     from llmserver_b200.ops.library import check_wait_errors
+    if prefill == "mma" and not (dim == vdim == 128):
+        pytest.skip("only heads of 128 have two prompt kernels to choose from")
     page_size = 16
     lengths = [300, 41, 1, 130, 2500]
     new_tokens = [1, 41, 1, 30, 1]
     queries = [(s, p) for s, (length, count) in enumerate(zip(lengths, new_tokens)) for p in range(length - count, length)]
     sinks = torch.linspace(-2.0, 3.0, heads)
-    for spike in ((len(queries) - 1, 15), (0, 16), None):
+    for spike in ((len(queries) - 1, 15), (0, 16), (60, 15), None):      # query 60: a prompt row at position 117
         q, k_pages, v_pages, tables, scale, want, spike_weight = _paged_attention_case(
             torch.bfloat16, heads, kv_heads, dim, vdim, lengths, queries, page_size, 23, sinks, spike)
         slices = [SequenceSlice(f"r{s}", [0] * count, length - count, [], [tables[s, :-(-length // page_size)].tolist()], 0)
@@ -280,8 +284,12 @@ def test_tensor_core_attention_with_sinks(heads, kv_heads, dim, vdim):
         width = (heads + kv_heads) * dim + kv_heads * vdim
         packed = torch.zeros((len(queries), width), dtype=torch.bfloat16)
         packed[:, :heads * dim] = q.reshape(len(queries), heads * dim)
-        out = ops.attention(packed.to(DEVICE), batch, batch.block_tables[0], k_pages.to(DEVICE), v_pages.to(DEVICE), heads, kv_heads,
-                            dim, scale, value_dim=vdim, sinks=sinks.to(DEVICE), precise=True)
+        before, attention_bf16.PRECISE_PREFILL_KERNEL = attention_bf16.PRECISE_PREFILL_KERNEL, prefill
+        try:
+            out = ops.attention(packed.to(DEVICE), batch, batch.block_tables[0], k_pages.to(DEVICE), v_pages.to(DEVICE), heads,
+                                kv_heads, dim, scale, value_dim=vdim, sinks=sinks.to(DEVICE), precise=True)
+        finally:
+            attention_bf16.PRECISE_PREFILL_KERNEL = before
         torch.cuda.synchronize()
         check_wait_errors()
         error = (out.cpu().double() - want).abs().max(dim=-1).values / want.abs().max(dim=-1).values.clamp_min(0.05)
