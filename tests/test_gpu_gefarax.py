@@ -523,6 +523,8 @@ def test_greedy_generation_through_the_engine(folders, name, dtype):
     prompts = [tokens_for(vocab, length, 50 + length) for length in (5, 23, 41, 9, 30)]
     engine = Engine(folders[name], max_new_tokens=10, max_batch_size=3, max_num_batched_tokens=32, prefill_chunk_size=12,
                     kv_cache_num_blocks=40, kv_cache_block_size=4, ignore_eos=True, dtype=dtype)
+    if name == "tensor_core_sizes":
+        engine.warmup()      # products tuned and decode graphs captured ahead of the first request
     generated = engine.generate(prompts)
     assert all(len(tokens) == 10 for tokens in generated)
     for prompt, tokens in zip(prompts, generated):
