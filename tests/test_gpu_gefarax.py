@@ -1,5 +1,6 @@
 """Gefarax on the GPU against the plain implementation in plain_gefarax.py: each mechanism alone, then whole models
 through the step function, the cache and the scheduler, cut and batched in different ways, in 32-bit and bfloat16."""
+import copy
 import json
 import math
 import os
@@ -31,6 +32,19 @@ SAFE_MARGIN = 0.03
 ALLOWED = {"float32": 2e-5, "bfloat16": 5e-2}
 
 
+def _every_expert(raw):
+    """The same model with routers that choose all of their experts: no routing decision is left that bfloat16
+    rounding could turn, so every row can be compared."""
+    changed = copy.deepcopy(raw)
+    for layer in changed["layers"]:
+        if layer["mlp"]:
+            layer["mlp"]["router"]["top"] = layer["mlp"]["router"]["experts"]
+    return changed
+
+
+EVERY_EXPERT = {name + "/every_expert": (_every_expert(raw), seed + 100) for name, (raw, seed) in GEFARAX.items()}
+
+
 # ------------------------------------------------------------------------------------------------ model folders
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
@@ -44,8 +58,8 @@ def folders(tmp_path_factory):
 
     root = tmp_path_factory.mktemp("gefarax")
     made = {}
-    for name, (raw, seed) in GEFARAX.items():
-        folder = write_model_folder(GefaraxConfig.from_dict(raw), str(root / name), seed, torch.bfloat16)
+    for name, (raw, seed) in list(GEFARAX.items()) + list(EVERY_EXPERT.items()):
+        folder = write_model_folder(GefaraxConfig.from_dict(raw), str(root / name.replace("/", "_")), seed, torch.bfloat16)
         path = os.path.join(folder, "model.safetensors")
         tensors = load_file(path)
         generator = torch.Generator().manual_seed(seed)
@@ -455,6 +469,27 @@ def test_mixed_batches_reuse_pages_and_slots(folders, name, dtype):
     # every layer run has a cache of its own: a looped layer holds one per pass
     runs = len(replayer.model.spec.schedule)
     assert sum(len(group.entries) for group in replayer.cache.groups) == runs
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_bfloat16_every_row_when_every_expert_is_chosen(folders, name):
+    """With nothing for rounding to turn, every bfloat16 row of a mixed trace and of a decoded tail must agree."""
+    folder = folders[name + "/every_expert"]
+    vocab = GEFARAX[name][0]["vocab"]
+    lengths = {"r0": 90, "r1": 47, "r2": 30, "r3": 101, "r4": 64}
+    requests = {key: tokens_for(vocab, length, 61 + index) for index, (key, length) in enumerate(lengths.items())}
+    records, peak = traces.mixed(requests, seed=8)
+    got, _ = run_in_process(folder, "bfloat16", records, peak)
+    want = traces.expected_rows(records, requests, lambda key: plain_logits(folder, requests[key])[0])
+    tokens = requests["r3"]
+    tail = traces.tail_decoded("r3", tokens, 40)
+    got_tail, _ = run_in_process(folder, "bfloat16", tail, traces.rounded(len(tokens)))
+    want_tail = traces.expected_rows(tail, {"r3": tokens}, lambda key: plain_logits(folder, tokens)[0])
+    for produced, expected in ((got, want), (got_tail, want_tail)):
+        assert set(produced) == set(expected)
+        for step in expected:
+            error = np.abs(produced[step] - expected[step]).max(axis=-1) / np.abs(expected[step]).max(axis=-1)
+            assert error.max() <= ALLOWED["bfloat16"], f"{name} step {step}: {error.max():.3e}"
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
