@@ -574,6 +574,30 @@ def test_greedy_generation_through_the_engine(folders, name, dtype):
     assert engine.cache.available() == engine.cache.capacity()
 
 
+def test_shared_prefix_pages_serve_every_pass_of_a_loop(folders):
+    """Two prompts that begin alike: the second takes the first one's complete pages over in every cache group (each
+    pass of a looped layer has pages of its own), computes only its own tail, and still generates the plain
+    implementation's tokens."""
+    from llmserver_b200 import Engine
+    name = "loop_in_the_middle"
+    vocab = GEFARAX[name][0]["vocab"]
+    shared = tokens_for(vocab, 24, 5)
+    prompts = [shared + tokens_for(vocab, 3, 6), shared + tokens_for(vocab, 9, 7)]
+    engine = Engine(folders[name], max_new_tokens=5, max_batch_size=2, max_num_batched_tokens=64, kv_cache_num_blocks=32,
+                    kv_cache_block_size=8, ignore_eos=True, dtype="float32")
+    first = engine.add_request(prompt_token_ids=prompts[0])
+    while first.status.value != "Decoding":
+        engine.step()
+    second = engine.add_request(prompt_token_ids=prompts[1])
+    while engine.step():
+        pass
+    assert engine.stats["prefill_tokens"] == len(prompts[0]) + len(prompts[1]) - 24
+    for prompt, request in zip(prompts, (first, second)):
+        logits, _ = plain_logits(folders[name], list(prompt) + list(request.generated_token_ids))
+        assert request.generated_token_ids == [int(logits[len(prompt) - 1 + index].argmax()) for index in range(5)]
+    engine.cache.check_invariants()
+
+
 def test_trace_run_program(folders, tmp_path):
     name, dtype = "loop_in_the_middle", "float32"
     vocab = GEFARAX[name][0]["vocab"]
