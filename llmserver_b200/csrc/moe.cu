@@ -138,32 +138,48 @@ __global__ void indexed_linear_kernel(const T* __restrict__ in, const T* __restr
     __syncthreads();
     const int expert = index ? index[pair] : 0;
     const T* matrix = weight + (size_t)expert * (GATED ? 2 : 1) * rows * inner;
-    const int first = blockIdx.y * warps * 4;       // four output elements per warp and block
-    for (int r = first + warp; r < min(first + warps * 4, rows); r += warps) {
-        const T* w = matrix + (size_t)r * inner;
-        float sum = 0.0f, sum_up = 0.0f;
-        if (inner % 8 == 0 && aligned16(weight)) {      // 16- or 32-byte runs per lane; the order depends on the inner size only
-            for (int i = lane * 8; i < inner; i += 256) {
-                float values[8], up_values[8];
-                load8<T>(w + i, values);
-                if (GATED) load8<T>(w + (size_t)rows * inner + i, up_values);
+    // four consecutive output elements per warp, worked on together so that their loads are in flight at the same time;
+    // each element's sum runs over k in an order that depends on the inner size alone
+    const int r0 = (blockIdx.y * warps + warp) * 4;
+    if (r0 >= rows) return;
+    float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sum_up[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (inner % 8 == 0 && aligned16(weight)) {      // 16- or 32-byte runs per lane
+        for (int i = lane * 8; i < inner; i += 256) {
+            float values[4][8], up_values[GATED ? 4 : 1][8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    sum = fmaf(in_row[i + j], values[j], sum);
-                    if (GATED) sum_up = fmaf(in_row[i + j], up_values[j], sum_up);
+            for (int q = 0; q < 4; ++q) {
+                const int r = min(r0 + q, rows - 1);      // a warp at the edge reads the last row again and drops it below
+                load8<T>(matrix + (size_t)r * inner + i, values[q]);
+                if (GATED) load8<T>(matrix + ((size_t)rows + r) * inner + i, up_values[q]);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float x = in_row[i + j];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    sum[q] = fmaf(x, values[q][j], sum[q]);
+                    if (GATED) sum_up[q] = fmaf(x, up_values[q][j], sum_up[q]);
                 }
             }
-        } else {
-            for (int i = lane; i < inner; i += 32) {
-                sum = fmaf(in_row[i], Num<T>::load(w + i), sum);
-                if (GATED) sum_up = fmaf(in_row[i], Num<T>::load(w + (size_t)rows * inner + i), sum_up);
+        }
+    } else {
+        for (int i = lane; i < inner; i += 32) {
+            const float x = in_row[i];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int r = min(r0 + q, rows - 1);
+                sum[q] = fmaf(x, Num<T>::load(matrix + (size_t)r * inner + i), sum[q]);
+                if (GATED) sum_up[q] = fmaf(x, Num<T>::load(matrix + ((size_t)rows + r) * inner + i), sum_up[q]);
             }
         }
-        sum = warp_sum(sum);
-        if (GATED) sum_up = warp_sum(sum_up);
-        if (lane == 0) {
-            const float value = GATED ? gated_activation(sum, sum_up, limit, alpha) : sum;
-            Num<O>::store(out + (size_t)pair * rows + r, value);
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float total = warp_sum(sum[q]);
+        const float total_up = GATED ? warp_sum(sum_up[q]) : 0.0f;
+        if (lane == 0 && r0 + q < rows) {
+            const float value = GATED ? gated_activation(total, total_up, limit, alpha) : total;
+            Num<O>::store(out + (size_t)pair * rows + r0 + q, value);
         }
     }
 }
