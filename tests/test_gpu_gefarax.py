@@ -574,6 +574,25 @@ def test_greedy_generation_through_the_engine(folders, name, dtype):
     assert engine.cache.available() == engine.cache.capacity()
 
 
+def test_running_out_of_pages_preempts_and_changes_no_token(folders):
+    """A pool too small for all requests: the youngest is put out, its pages (of every pass of the looped layer) come
+    back, its cache is rebuilt later; in 32-bit no token changes, and temperature sampling gives the same draws."""
+    from llmserver_b200 import Engine
+    name = "loop_from_start"
+    vocab = GEFARAX[name][0]["vocab"]
+    prompts = [tokens_for(vocab, length, 70 + length) for length in (30, 21, 44, 9)]
+    roomy = Engine(folders[name], max_new_tokens=40, max_batch_size=4, max_num_batched_tokens=32, kv_cache_num_blocks=128,
+                   kv_cache_block_size=4, ignore_eos=True, dtype="float32")
+    expected = roomy.generate(prompts, temperature=0.7, seed=3)
+    assert roomy.stats["preemptions"] == 0
+    tight = Engine(roomy.model, max_new_tokens=40, max_batch_size=4, max_num_batched_tokens=32, kv_cache_num_blocks=48,
+                   kv_cache_block_size=4, ignore_eos=True)
+    assert tight.generate(prompts, temperature=0.7, seed=3) == expected
+    assert tight.stats["preemptions"] > 0
+    tight.cache.check_invariants()
+    assert tight.cache.available() == tight.cache.capacity()
+
+
 def test_shared_prefix_pages_serve_every_pass_of_a_loop(folders):
     """Two prompts that begin alike: the second takes the first one's complete pages over in every cache group (each
     pass of a looped layer has pages of its own), computes only its own tail, and still generates the plain
