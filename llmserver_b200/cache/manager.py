@@ -29,13 +29,17 @@ RELEASED = -1  # block-table entry of a page the window has passed
 class KVPagesNeed:
     """Keys and values of ``kv_heads`` heads of ``head_dim``; ``window`` None keeps all tokens,
     else only the last ``window`` tokens are ever read.  ``value_dim``: the size of a value head where it differs
-    from a key head's (None: the same)."""
+    from a key head's (None: the same).  ``keys_only``: what is cached serves as key and as value (a latent from which
+    both are made): one tensor is kept and handed out as both."""
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
     value_dim: Optional[int] = None
+    keys_only: bool = False
 
     def __post_init__(self):
+        if self.keys_only and self.value_dim is not None:
+            raise ValueError("a cache of keys alone has no value size of its own")
         if self.value_dim is not None and int(self.value_dim) == int(self.head_dim):
             object.__setattr__(self, "value_dim", None)     # one spelling per shape, so that equal needs share a group
 
@@ -154,7 +158,9 @@ class CacheManager:
         for group in self.groups:
             need = group.need
             shape = (len(group.entries), group.pool.num_pages, need.kv_heads, self.page_size)
-            if need.value_dim is None:
+            if need.keys_only:
+                group.key_storage = group.value_storage = torch.zeros(shape + (need.head_dim,), dtype=dtype, device=device)
+            elif need.value_dim is None:
                 group.storage = torch.zeros((shape[0], 2) + shape[1:] + (need.head_dim,), dtype=dtype, device=device)
                 group.key_storage, group.value_storage = group.storage[:, 0], group.storage[:, 1]
             else:
@@ -176,7 +182,7 @@ class CacheManager:
     def storage_bytes(self) -> int:
         total = 0
         for group in self.groups:
-            for tensor in (group.key_storage, group.value_storage):
+            for tensor in (group.key_storage,) if group.value_storage is group.key_storage else (group.key_storage, group.value_storage):
                 if tensor is not None:
                     total += tensor.numel() * tensor.element_size()
         return total

@@ -3,7 +3,8 @@ from .spec import PartSpec, LayerSpec, ScheduleEntry, ModelSpec
 from .registry import ARCHITECTURES, Architecture, register_architecture, architecture_of, read_config
 from .qwen3 import Qwen3Config, FULL_ATTENTION, SLIDING_ATTENTION
 from .gefarax import GefaraxConfig
+from .dikusun import DikusunConfig
 
 __all__ = ["UnsupportedModelError", "WeightLoadError", "PartSpec", "LayerSpec", "ScheduleEntry", "ModelSpec",
            "ARCHITECTURES", "Architecture", "register_architecture", "architecture_of", "read_config",
-           "Qwen3Config", "GefaraxConfig", "FULL_ATTENTION", "SLIDING_ATTENTION"]
+           "Qwen3Config", "GefaraxConfig", "DikusunConfig", "FULL_ATTENTION", "SLIDING_ATTENTION"]

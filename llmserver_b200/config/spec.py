@@ -84,6 +84,7 @@ class ModelSpec:
     final_norm_prefix: str = "model.norm."
     head_name: str = "lm_head.weight"
     tie_head: bool = False
+    embedding_scale: float = 1.0    # the embedded tokens are multiplied by this as they enter the stream
     max_positions: Optional[int] = None
     eos_token_ids: Tuple[int, ...] = ()
     notes: dict = field(default_factory=dict)

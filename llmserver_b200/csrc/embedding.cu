@@ -1,10 +1,11 @@
 // Token embedding: residual[n, :] = table[ids[n], :], widened to the 32-bit residual stream.
-// The reference does a plain row lookup with no scaling (utils/model.py:56-59,110).
+// The reference does a plain row lookup with no scaling (utils/model.py:56-59,110); `scale` multiplies the row for
+// models that scale their embedding (1 elsewhere).
 #include "common.cuh"
 
 template <typename T>
 __global__ void embedding_gather_kernel(float* __restrict__ out, const T* __restrict__ table,
-                                        const int* __restrict__ ids, int hidden, int vocab, int vector_form) {
+                                        const int* __restrict__ ids, int hidden, int vocab, int vector_form, float scale) {
     pdl_trigger();   // let the next kernel start launching
     pdl_wait();      // everything before this kernel in the stream is complete and visible
     const int token = blockIdx.x;
@@ -17,20 +18,22 @@ __global__ void embedding_gather_kernel(float* __restrict__ out, const T* __rest
         for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
             float values[8];
             load8<T>(row + i, values);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) values[j] *= scale;
             store8<float>(dst + i, values);
         }
     } else {
-        for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = Num<T>::load(row + i);
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = Num<T>::load(row + i) * scale;
     }
 }
 
 LLM_EXPORT int llm_embedding_gather(float* out, const void* table, const int* ids, int n_tokens, int hidden,
-                                    int vocab, int dtype, cudaStream_t stream) {
+                                    int vocab, int dtype, float scale, cudaStream_t stream) {
     if (n_tokens == 0) return LLM_OK;
     const int vector_form = hidden % 8 == 0 && aligned16(out) && aligned16(table);
     int threads = vector_form ? (hidden / 8 + 31) / 32 * 32 : (hidden >= 1024 ? 256 : 128);
     if (threads > 512) threads = 512;
     LLM_DISPATCH_DTYPE(dtype, (llm_launch(embedding_gather_kernel<T>, n_tokens, threads, 0, stream, 
-                                  out, (const T*)table, ids, hidden, vocab, vector_form)));
+                                  out, (const T*)table, ids, hidden, vocab, vector_form, scale)));
     return llm_check_launch("embedding_gather");
 }

@@ -159,15 +159,17 @@ LLM_EXPORT int llm_rmsnorm(const void* x, const void* weight, void* out, int n_r
 }
 
 // A sub-layer whose output is normalised before it joins the stream, fused with the norm that follows:
-//   residual[r] += delta[r] * rsqrt(mean(delta[r]^2) + post_eps) * post_weight (+ extra[r])
+//   residual[r] += d * rsqrt(mean(d^2) + post_eps) * post_weight (+ extra[r]),  d = delta[r] (+ delta_bias)
 //   out[o]       = residual[r] * rsqrt(mean(residual[r]^2) + eps) * weight          (skipped when out is null)
+// `delta_bias` (32-bit, [width]) is the bias of the projection that made delta, added here in 32-bit.  Without `weight`
+// the output is the updated stream itself in the activation type: what a sub-layer reads that takes the stream as it is.
 // `extra` is a second 32-bit stream added at the same time (a model that feeds its embedding in again).  Both
 // statistics, both products and the sum are 32-bit; the updated row waits in shared memory between the passes.
 template <typename T, typename W>
 __global__ void normed_add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                           const W* __restrict__ post_weight, float post_eps, const float* __restrict__ extra,
                                           const W* __restrict__ weight, T* __restrict__ out, const int* __restrict__ rows,
-                                          int width, float eps, int write_residual) {
+                                          int width, float eps, int write_residual, const float* __restrict__ delta_bias) {
     pdl_trigger();
     pdl_wait();
     __shared__ float scratch[33];
@@ -180,7 +182,7 @@ __global__ void normed_add_rmsnorm_kernel(float* __restrict__ residual, const T*
         const T* del = delta + (size_t)r * width;
         float sum_squares = 0.0f;
         for (int i = threadIdx.x; i < width; i += blockDim.x) {
-            const float v = Num<T>::load(del + i);
+            const float v = Num<T>::load(del + i) + (delta_bias ? delta_bias[i] : 0.0f);
             updated[i] = v;
             sum_squares += v * v;
         }
@@ -196,8 +198,12 @@ __global__ void normed_add_rmsnorm_kernel(float* __restrict__ residual, const T*
         sum_squares += v * v;
     }
     if (!out) return;
-    const float inverse = rsqrtf(block_sum(sum_squares, scratch) / (float)width + eps);
     T* dst = out + (size_t)o * width;
+    if (!weight) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) Num<T>::store(dst + i, updated[i]);
+        return;
+    }
+    const float inverse = rsqrtf(block_sum(sum_squares, scratch) / (float)width + eps);
     for (int i = threadIdx.x; i < width; i += blockDim.x)
         Num<T>::store(dst + i, updated[i] * inverse * Num<W>::load(weight + i));
 }
@@ -208,7 +214,7 @@ template <typename T, typename W>
 __global__ void normed_add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                               const W* __restrict__ post_weight, float post_eps, const float* __restrict__ extra,
                                               const W* __restrict__ weight, T* __restrict__ out, const int* __restrict__ rows,
-                                              int width, float eps, int write_residual) {
+                                              int width, float eps, int write_residual, const float* __restrict__ delta_bias) {
     pdl_trigger();
     pdl_wait();
     __shared__ float scratch[33];
@@ -226,6 +232,12 @@ __global__ void normed_add_rmsnorm_vec_kernel(float* __restrict__ residual, cons
             const int c = threadIdx.x + i * blockDim.x;
             if (c < chunks) {
                 load8<T>(del + c * kChunk, values[i]);
+                if (delta_bias) {
+                    float bias[kChunk];
+                    load8<float>(delta_bias + c * kChunk, bias);
+#pragma unroll
+                    for (int j = 0; j < kChunk; ++j) values[i][j] += bias[j];
+                }
 #pragma unroll
                 for (int j = 0; j < kChunk; ++j) sum_squares += values[i][j] * values[i][j];
             }
@@ -260,8 +272,16 @@ __global__ void normed_add_rmsnorm_vec_kernel(float* __restrict__ residual, cons
         }
     }
     if (!out) return;
-    const float inverse = rsqrtf(block_sum(sum_squares, scratch) / (float)width + eps);
     T* dst = out + (size_t)o * width;
+    if (!weight) {
+#pragma unroll
+        for (int i = 0; i < kMaxChunks; ++i) {
+            const int c = threadIdx.x + i * blockDim.x;
+            if (c < chunks) store8<T>(dst + c * kChunk, values[i]);
+        }
+        return;
+    }
+    const float inverse = rsqrtf(block_sum(sum_squares, scratch) / (float)width + eps);
 #pragma unroll
     for (int i = 0; i < kMaxChunks; ++i) {
         const int c = threadIdx.x + i * blockDim.x;
@@ -278,26 +298,22 @@ __global__ void normed_add_rmsnorm_vec_kernel(float* __restrict__ residual, cons
 LLM_EXPORT int llm_normed_add_rmsnorm(float* residual, const void* delta, const void* post_weight, float post_eps,
                                       const float* extra, const void* weight, void* out, const int* rows, int n_rows,
                                       int width, float eps, int write_residual, int dtype, int weight_dtype,
-                                      cudaStream_t stream) {
+                                      const float* delta_bias, cudaStream_t stream) {
     if (n_rows == 0) return LLM_OK;
     if (delta && !post_weight) {
         llm_set_error("normed_add_rmsnorm: a delta needs the weight of its norm");
-        return LLM_REFUSED;
-    }
-    if (out && !weight) {
-        llm_set_error("normed_add_rmsnorm: an output needs the weight of its norm");
         return LLM_REFUSED;
     }
     const int chunks = width / kChunk;
     int threads = ((chunks + 31) / 32) * 32;      // depends on the width only
     if (threads > 512) threads = 512;
     const bool vector_form = width % kChunk == 0 && width >= kChunk && chunks <= threads * kMaxChunks && aligned16(residual) &&
-                             aligned16(delta) && aligned16(post_weight) && aligned16(extra) && aligned16(weight) && aligned16(out);
+                             aligned16(delta) && aligned16(post_weight) && aligned16(extra) && aligned16(weight) && aligned16(out) && aligned16(delta_bias);
     if (vector_form) {
         LLM_DISPATCH_DTYPE_WEIGHT(dtype, weight_dtype,
                                   (llm_launch(normed_add_rmsnorm_vec_kernel<T, W>, n_rows, threads, 0, stream, residual,
                                       (const T*)delta, (const W*)post_weight, post_eps, extra, (const W*)weight, (T*)out, rows,
-                                      width, eps, write_residual)));
+                                      width, eps, write_residual, delta_bias)));
         return llm_check_launch("normed_add_rmsnorm");
     }
     const size_t shared = (size_t)width * sizeof(float);
@@ -311,7 +327,7 @@ LLM_EXPORT int llm_normed_add_rmsnorm(float* residual, const void* delta, const 
             if (status != LLM_OK) return status;
         }
         llm_launch(normed_add_rmsnorm_kernel<T, W>, n_rows, norm_threads(width), shared, stream, residual, (const T*)delta,
-                   (const W*)post_weight, post_eps, extra, (const W*)weight, (T*)out, rows, width, eps, write_residual);
+                   (const W*)post_weight, post_eps, extra, (const W*)weight, (T*)out, rows, width, eps, write_residual, delta_bias);
     });
     return llm_check_launch("normed_add_rmsnorm");
 }

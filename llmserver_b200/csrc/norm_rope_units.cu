@@ -1,0 +1,141 @@
+// Bias + per-unit RMSNorm + rotary positions + paged K/V write for projections whose heads are made of several
+// units, with query units, key units and value heads of three different sizes.
+//
+// The packed projection of a token is [Hq * M * Dq | Hkv * M * Dk | Hkv * Dv | ...]: every query head and every key
+// head consists of M units ("maps": a head that attends with several score maps has one query and one key unit per
+// map; M = 1 is the ordinary head).  Columns behind the values are left alone.  One warp per (token, unit):
+//   1. the unit's elements, plus the projection's bias where there is one, in 32-bit;
+//   2. RMSNorm over the unit with a weight shared by all units of its kind (`q_weight` [Dq], `k_weight` [Dk]);
+//   3. the first `rotary_dim` elements rotated, element i paired with i + rotary_dim / 2:
+//        (u, v) -> (u cos a - v sin a, v cos a + u sin a),  a = position * inv_freq[i];
+//   4. query units written back where they lie, or packed into `q_out` [N, Hq * M * Dq]; key units written into
+//      the token's slot of the K pages [page, Hkv, slot, M * Dk]; value heads (bias added) into the V pages
+//      [page, Hkv, slot, Dv].
+// Each of bias, norms, rotation and values may be absent (Dv = 0: a cache of keys alone, as for a latent that serves as
+// key and value).  Sums, angles and products are 32-bit; every element is rounded once, when it is stored.
+#include "common.cuh"
+
+template <typename T, typename W>
+__global__ void norm_rope_units_kernel(T* __restrict__ qkv, int row_width, const float* __restrict__ bias,
+                                       const W* __restrict__ q_weight, const W* __restrict__ k_weight, float eps,
+                                       const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                                       const int* __restrict__ seq_of_token, const int* __restrict__ block_tables,
+                                       int max_blocks, T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                       int n_q_heads, int n_kv_heads, int maps, int q_dim, int k_dim, int value_dim,
+                                       int page_size, int num_pages, int write_cache, int* __restrict__ error_flag,
+                                       int rotary_dim, int max_dim) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float unit_values[];     // [warps][max_dim]
+    const int token = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    float* values = unit_values + (size_t)warp * max_dim;
+    const int position = positions[token];
+    const int q_units = n_q_heads * maps, k_units = n_kv_heads * maps;
+    const int total_units = q_units + k_units + (value_dim > 0 ? n_kv_heads : 0);
+    T* row = qkv + (size_t)token * row_width;
+    const int half = rotary_dim >> 1;
+    for (int unit = blockIdx.y * warps + warp; unit < total_units; unit += gridDim.y * warps) {
+        const bool is_q = unit < q_units;
+        const bool is_k = !is_q && unit < q_units + k_units;
+        int dim, column;
+        if (is_q) {
+            dim = q_dim;
+            column = unit * q_dim;
+        } else if (is_k) {
+            dim = k_dim;
+            column = q_units * q_dim + (unit - q_units) * k_dim;
+        } else {
+            dim = value_dim;
+            column = q_units * q_dim + k_units * k_dim + (unit - q_units - k_units) * value_dim;
+        }
+        T* dst;
+        if (is_q) {
+            dst = q_out ? q_out + (size_t)token * q_units * q_dim + (size_t)unit * q_dim : row + column;
+        } else {
+            if (!write_cache) continue;
+            const int page = block_tables[(size_t)seq_of_token[token] * max_blocks + position / page_size];
+            if (page < 0 || page >= num_pages) {
+                if (lane == 0) atomicExch(error_flag, 1 + token);   // the host turns this into an exception
+                continue;
+            }
+            if (is_k) {
+                const int k_unit = unit - q_units;
+                const size_t slot = ((size_t)page * n_kv_heads + k_unit / maps) * page_size + position % page_size;
+                dst = k_pages + slot * ((size_t)maps * k_dim) + (size_t)(k_unit % maps) * k_dim;
+            } else {
+                const size_t slot = ((size_t)page * n_kv_heads + (unit - q_units - k_units)) * page_size + position % page_size;
+                dst = v_pages + slot * value_dim;
+            }
+        }
+        float sum_squares = 0.0f;
+        for (int i = lane; i < dim; i += 32) {
+            float v = Num<T>::load(row + column + i);
+            if (bias) v += bias[column + i];
+            values[i] = v;
+            sum_squares += v * v;
+        }
+        const W* weight = is_q ? q_weight : (is_k ? k_weight : nullptr);
+        if (weight) {
+            const float inverse = rsqrtf(warp_sum(sum_squares) / (float)dim + eps);
+            for (int i = lane; i < dim; i += 32) values[i] = values[i] * inverse * Num<W>::load(weight + i);
+        }
+        __syncwarp();
+        const int turning = (inv_freq && (is_q || is_k)) ? rotary_dim : 0;
+        for (int i = lane; i < turning / 2; i += 32) {
+            const float angle = (float)position * inv_freq[i];
+            const float c = cosf(angle), s = sinf(angle);
+            const float u = values[i], v = values[half + i];
+            Num<T>::store(dst + i, u * c - v * s);
+            Num<T>::store(dst + half + i, v * c + u * s);
+        }
+        for (int i = turning + lane; i < dim; i += 32) Num<T>::store(dst + i, values[i]);
+        __syncwarp();      // the next unit of this warp overwrites the values
+    }
+}
+
+LLM_EXPORT int llm_norm_rope_units(void* qkv, int row_width, const float* bias, const void* q_weight, const void* k_weight,
+                                   float eps, const float* inv_freq, const int* positions, const int* seq_of_token,
+                                   const int* block_tables, int max_blocks, void* q_out, void* k_pages, void* v_pages,
+                                   int n_tokens, int n_q_heads, int n_kv_heads, int maps, int q_dim, int k_dim, int value_dim,
+                                   int page_size, int num_pages, int write_cache, int* error_flag, int rotary_dim, int dtype,
+                                   int weight_dtype, cudaStream_t stream) {
+    if (n_tokens == 0) return LLM_OK;
+    if (inv_freq == nullptr) rotary_dim = 0;
+    if (n_q_heads <= 0 || n_kv_heads <= 0 || maps <= 0 || q_dim <= 0 || k_dim <= 0 || value_dim < 0 || page_size <= 0 || num_pages <= 0) {
+        llm_set_error("norm_rope_units: sizes must be positive (value_dim may be 0)");
+        return LLM_REFUSED;
+    }
+    if (rotary_dim < 0 || rotary_dim % 2 || rotary_dim > q_dim || rotary_dim > k_dim) {
+        llm_set_error("norm_rope_units: rotary_dim must be even and at most the unit sizes %d and %d, got %d", q_dim, k_dim, rotary_dim);
+        return LLM_REFUSED;
+    }
+    const long long used = (long long)(n_q_heads * maps) * q_dim + (long long)(n_kv_heads * maps) * k_dim + (long long)n_kv_heads * value_dim;
+    if (row_width < used) {
+        llm_set_error("norm_rope_units: rows of %d columns cannot hold %lld", row_width, used);
+        return LLM_REFUSED;
+    }
+    int max_dim = q_dim > k_dim ? q_dim : k_dim;
+    if (value_dim > max_dim) max_dim = value_dim;
+    const int warps = 4;
+    const size_t shared = (size_t)warps * max_dim * sizeof(float);
+    if (shared > 160 * 1024) {
+        llm_set_error("norm_rope_units: units of %d elements need %zu bytes of shared memory", max_dim, shared);
+        return LLM_REFUSED;
+    }
+    const int total_units = (n_q_heads + n_kv_heads) * maps + (value_dim > 0 ? n_kv_heads : 0);
+    int slices = (total_units + warps - 1) / warps;
+    if (n_tokens >= 1024 && slices > 2) slices = 2;      // long prompts: fewer, longer-lived blocks
+    dim3 grid(n_tokens, slices);
+    LLM_DISPATCH_DTYPE_WEIGHT(dtype, weight_dtype, {
+        if (shared > 40 * 1024) {
+            const int status = llm_raise_shared_limit((const void*)norm_rope_units_kernel<T, W>, shared, "norm_rope_units");
+            if (status != LLM_OK) return status;
+        }
+        llm_launch(norm_rope_units_kernel<T, W>, grid, warps * 32, shared, stream, (T*)qkv, row_width, bias, (const W*)q_weight,
+                   (const W*)k_weight, eps, inv_freq, positions, seq_of_token, block_tables, max_blocks, (T*)q_out, (T*)k_pages,
+                   (T*)v_pages, n_q_heads, n_kv_heads, maps, q_dim, k_dim, value_dim, page_size, num_pages, write_cache, error_flag,
+                   rotary_dim, max_dim);
+    });
+    return llm_check_launch("norm_rope_units");
+}

@@ -76,7 +76,7 @@ class DecoderModel:
     def step(self, batch) -> torch.Tensor:
         if self.entry_caches is None:
             raise RuntimeError("bind_cache() has to be called before the first step")
-        residual = ops.embedding(self.embedding, batch.token_ids)
+        residual = ops.embedding(self.embedding, batch.token_ids, scale=self.spec.embedding_scale)
         for position in self.positions.values():
             position.on_embedding(residual, batch)
         delta = None
@@ -84,7 +84,7 @@ class DecoderModel:
         embedded = None
         if any(entry.add_embedding for entry in schedule):
             # the stream is updated in place, so entries that take the embedded tokens in again read a second gather
-            embedded = ops.embedding(self.embedding, batch.token_ids)
+            embedded = ops.embedding(self.embedding, batch.token_ids, scale=self.spec.embedding_scale)
             for position in self.positions.values():
                 position.on_embedding(embedded, batch)
         for index, entry in enumerate(schedule):

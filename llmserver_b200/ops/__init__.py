@@ -20,11 +20,12 @@ __all__ = ["KernelError", "embedding", "add_rmsnorm", "rmsnorm", "silu_mul", "sa
            "attention_generic", "rope_kv_write_split", "normed_add_rmsnorm", "moe_route", "moe_select", "indexed_linear", "moe_combine", "moe_plan", "moe_grouped",
            "moe_grouped_supported", "moe_combine_rows", "ExpertPlan",
            "clamped_glu", "gemm_f32", "linear", "linear_wide", "qkv_projection", "gate_up_silu", "interleave_gate_up", "require_device", "library", "launch_count",
-           "RowScaled", "StreamSink", "STREAM_ROWS", "unscaled_rows_supported"]
+           "RowScaled", "StreamSink", "STREAM_ROWS", "unscaled_rows_supported", "norm_rope_units", "attention_diff", "gla_supported",
+           "gla_recurrent", "head_linear"]
 
 
-def embedding(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """residual[n] = table[ids[n]] widened to float32.  ids: int32 [N]."""
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
+    """residual[n] = table[ids[n]] * scale, widened to float32.  ids: int32 [N]."""
     check(table, "embedding table")
     check(ids, "token ids", torch.int32)
     vocab, hidden = table.shape
@@ -33,7 +34,7 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor
         out = torch.empty((tokens, hidden), dtype=torch.float32, device=table.device)
     check(out, "embedding output", torch.float32, hidden)
     call("llm_embedding_gather", out.data_ptr(), table.data_ptr(), ids.data_ptr(), tokens, hidden, vocab,
-         dtype_code(table.dtype), stream_handle())
+         dtype_code(table.dtype), float(scale), stream_handle())
     return out
 
 
@@ -260,14 +261,17 @@ def rope_kv_write_split(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], mag
 def normed_add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], post_weight: Optional[torch.Tensor],
                        post_eps: float, weight: Optional[torch.Tensor], eps: float, extra: Optional[torch.Tensor] = None,
                        rows: Optional[torch.Tensor] = None, act_dtype: Optional[torch.dtype] = None,
-                       want_output: bool = True) -> Optional[torch.Tensor]:
-    """residual += rmsnorm(delta) * post_weight (+ extra), all 32-bit and in place; then, unless ``want_output`` is
-    False, returns rmsnorm(residual) * weight in the activation type.  ``delta`` (activation type) and ``extra``
-    (float32, the stream's shape) may each be absent.  With ``rows`` (int32) output row o comes from row rows[o] and
-    the stream is left as it was."""
+                       want_output: bool = True, delta_bias: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """residual += rmsnorm(delta + delta_bias) * post_weight (+ extra), all 32-bit and in place; then, unless
+    ``want_output`` is False, returns rmsnorm(residual) * weight in the activation type, or, without a ``weight``, the
+    updated stream itself in the activation type.  ``delta`` (activation type), ``delta_bias`` (float32 [width]: the bias
+    of the projection that made delta) and ``extra`` (float32, the stream's shape) may each be absent.  With ``rows``
+    (int32) output row o comes from row rows[o] and the stream is left as it was."""
     check(residual, "residual", torch.float32)
     width = residual.shape[-1]
     act = act_dtype or (delta.dtype if delta is not None else weight.dtype)
+    if delta_bias is not None:
+        check(delta_bias, "delta bias", torch.float32, width)
     weight_dtype = None
     for name, tensor in (("post-norm weight", post_weight), ("norm weight", weight)):
         if tensor is not None:
@@ -292,8 +296,151 @@ def normed_add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], po
     out = torch.empty((n_rows, width), dtype=act, device=residual.device) if want_output else None
     call("llm_normed_add_rmsnorm", residual.data_ptr(), pointer(delta), pointer(post_weight), float(post_eps), pointer(extra),
          pointer(weight), pointer(out), pointer(rows), n_rows, width, float(eps), int(write_residual), dtype_code(act),
-         dtype_code(weight_dtype if weight_dtype is not None else act), stream_handle())
+         dtype_code(weight_dtype if weight_dtype is not None else act), pointer(delta_bias), stream_handle())
     return out
+
+
+def norm_rope_units(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_tables: torch.Tensor,
+                    k_pages: torch.Tensor, v_pages: Optional[torch.Tensor], n_q_heads: int, n_kv_heads: int, maps: int,
+                    q_dim: int, k_dim: int, value_dim: int, error_flag: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                    q_weight: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
+                    inv_freq: Optional[torch.Tensor] = None, rotary_dim: int = 0, q_out: Optional[torch.Tensor] = None,
+                    write_cache: bool = True) -> None:
+    """On the packed projection ``qkv`` [N, >= (Hq M Dq + Hkv M Dk + Hkv Dv)], whose query and key heads consist of
+    ``maps`` units each: per unit the projection's ``bias`` (float32, over the q, k and v columns) is added, the unit
+    RMS-normalised with the weight of its kind ([Dq] / [Dk], shared by all units), and its first ``rotary_dim`` elements
+    rotated (element i with i + rotary_dim / 2, angle position * inv_freq[i]).  Query units are written back in place,
+    or packed into ``q_out`` [N, Hq M Dq]; key units go to the K pages [page, Hkv, slot, M Dk], value heads (bias added)
+    to the V pages [page, Hkv, slot, Dv].  ``value_dim`` 0: there are no values.  Everything in 32-bit, one rounding."""
+    check(qkv, "qkv")
+    tokens, row_width = qkv.shape
+    weight_dtype = qkv.dtype
+    for name, tensor, size in (("q norm weight", q_weight, q_dim), ("k norm weight", k_weight, k_dim)):
+        if tensor is not None:
+            check(tensor, name, last_dim=size)
+            weight_dtype = tensor.dtype
+    if q_weight is not None and k_weight is not None and q_weight.dtype != k_weight.dtype:
+        raise KernelError("q and k norm weights must share a dtype")
+    used = (n_q_heads * q_dim + n_kv_heads * k_dim) * maps + n_kv_heads * value_dim
+    if bias is not None:
+        check(bias, "projection bias", torch.float32)
+        if bias.numel() < used:
+            raise KernelError(f"the bias holds {bias.numel()} numbers; the q, k and v columns are {used}")
+    if inv_freq is not None:
+        check(inv_freq, "inv_freq", torch.float32, rotary_dim // 2)
+    check(positions, "positions", torch.int32)
+    check(seq_of_token, "seq_of_token", torch.int32)
+    check(block_tables, "block_tables", torch.int32)
+    check(k_pages, "k pages", qkv.dtype, maps * k_dim)
+    if value_dim:
+        check(v_pages, "v pages", qkv.dtype, value_dim)
+        if k_pages.shape[:-1] != v_pages.shape[:-1]:
+            raise KernelError(f"k pages {tuple(k_pages.shape)} and v pages {tuple(v_pages.shape)} differ in more than the last dimension")
+    if k_pages.dim() != 4 or k_pages.shape[1] != n_kv_heads:
+        raise KernelError(f"pages must be [pages, {n_kv_heads}, page_size, ...], got {tuple(k_pages.shape)}")
+    if q_out is not None:
+        check(q_out, "packed queries", qkv.dtype, n_q_heads * maps * q_dim)
+    if positions.numel() != tokens or seq_of_token.numel() != tokens:
+        raise KernelError("positions and seq_of_token need one entry per token")
+    check(error_flag, "error flag", torch.int32)
+    call("llm_norm_rope_units", qkv.data_ptr(), row_width, pointer(bias), pointer(q_weight), pointer(k_weight), float(eps),
+         pointer(inv_freq), positions.data_ptr(), seq_of_token.data_ptr(), block_tables.data_ptr(), block_tables.shape[-1],
+         pointer(q_out), k_pages.data_ptr(), pointer(v_pages) if value_dim else 0, tokens, n_q_heads, n_kv_heads, int(maps),
+         int(q_dim), int(k_dim), int(value_dim), k_pages.shape[2], k_pages.shape[0], int(write_cache), error_flag.data_ptr(),
+         int(rotary_dim) if inv_freq is not None else 0, dtype_code(qkv.dtype), dtype_code(weight_dtype), stream_handle())
+
+
+def attention_diff(qkv: torch.Tensor, gate_column: Optional[int], batch, block_tables: torch.Tensor, k_pages: torch.Tensor,
+                   v_pages: torch.Tensor, n_q_heads: int, n_kv_heads: int, dim: int, value_dim: int, scale: float, cap: float,
+                   window: int, lam: float, eps: float, out_scale: float) -> torch.Tensor:
+    """Differential attention of a step's tokens over the paged cache.  ``qkv`` [N, row] holds each token's query heads
+    first, a head as [map 1 | map 2] of ``dim`` elements each, already normalised and rotated; K pages hold key heads
+    in the same form, V pages value heads of ``value_dim``.  Per head: a_m = softmax(cap(q_m . k_m * scale)) V over keys
+    p - window + 1 .. p (window 0: all), o = a_1 - lam * a_2, out = o / sqrt(mean(o^2) + eps) * out_scale, times
+    sigmoid(qkv[n, gate_column + head]) when ``gate_column`` is given.  Returns [N, Hq * value_dim]."""
+    check(qkv, "qkv")
+    tokens, row_width = qkv.shape
+    check(k_pages, "k pages", qkv.dtype, 2 * dim)
+    check(v_pages, "v pages", qkv.dtype, value_dim)
+    if k_pages.shape[:-1] != v_pages.shape[:-1] or k_pages.shape[1] != n_kv_heads:
+        raise KernelError(f"k pages {tuple(k_pages.shape)} and v pages {tuple(v_pages.shape)} do not fit {n_kv_heads} kv heads")
+    check(block_tables, "block_tables", torch.int32)
+    out = torch.empty((tokens, n_q_heads * value_dim), dtype=qkv.dtype, device=qkv.device)
+    if qkv.dtype == torch.bfloat16:
+        from . import attention_bf16
+        if attention_bf16.try_attention_diff(qkv, gate_column, batch, block_tables, k_pages, v_pages, n_q_heads, n_kv_heads, dim,
+                                             value_dim, scale, cap, window, lam, eps, out_scale, out):
+            return out
+    gate = 0 if gate_column is None else qkv.data_ptr() + gate_column * qkv.element_size()
+    call("llm_attention_diff", qkv.data_ptr(), row_width, gate, row_width, k_pages.data_ptr(), v_pages.data_ptr(),
+         block_tables.data_ptr(), block_tables.shape[-1], batch.seq_of_token.data_ptr(), batch.positions.data_ptr(),
+         out.data_ptr(), tokens, n_q_heads, n_kv_heads, int(dim), int(value_dim), k_pages.shape[2], k_pages.shape[0],
+         float(scale), float(cap or 0.0), int(window or 0), float(lam), float(eps), float(out_scale),
+         wait_error_flag(qkv.device).data_ptr(), dtype_code(qkv.dtype), stream_handle())
+    return out
+
+
+def gla_supported(dim: int, value_dim: int) -> bool:
+    return bool(library().llm_gla_supports(int(dim), int(value_dim)))
+
+
+def gla_recurrent(proj: torch.Tensor, q_column: int, k_column: int, v_column: int, g_column: int, z: torch.Tensor,
+                  z_bias: Optional[torch.Tensor], weight: torch.Tensor, state: torch.Tensor, batch, heads: int, dim: int,
+                  value_dim: int, tau: float, q_scale: float, eps: float) -> torch.Tensor:
+    """The gated-linear-attention recurrence over a step's tokens, sequence by sequence, from and into each sequence's
+    slot of ``state`` (float32 [slots, heads, dim, value_dim]):
+
+        alpha = sigmoid(z + z_bias) ^ (1 / tau);  S <- diag(alpha) S + k v^T;  o = S^T (q * q_scale)
+        out   = o / sqrt(mean(o^2) + eps) * weight * silu(g)          per head, over value_dim
+
+    q, k (heads * dim columns each), v and g (heads * value_dim) start at the given columns of ``proj``; ``z`` is
+    [N, heads * dim].  Returns [N, heads * value_dim] in the activation type; the recurrence itself is 32-bit."""
+    check(proj, "packed projection")
+    tokens, row_width = proj.shape
+    check(z, "decay projection", proj.dtype, heads * dim)
+    if z_bias is not None:
+        check(z_bias, "decay bias", torch.float32, heads * dim)
+    check(weight, "norm weight", last_dim=value_dim)
+    check(state, "recurrent state", torch.float32, value_dim)
+    if state.dim() != 4 or tuple(state.shape[1:]) != (heads, dim, value_dim):
+        raise KernelError(f"the state must be [slots, {heads}, {dim}, {value_dim}], got {tuple(state.shape)}")
+    for column, size in ((q_column, heads * dim), (k_column, heads * dim), (v_column, heads * value_dim), (g_column, heads * value_dim)):
+        if column < 0 or column + size > row_width:
+            raise KernelError(f"columns {column}..{column + size} lie outside a row of {row_width}")
+    out = torch.empty((tokens, heads * value_dim), dtype=proj.dtype, device=proj.device)
+    call("llm_gla_recurrent", proj.data_ptr(), row_width, int(q_column), int(k_column), int(v_column), int(g_column),
+         z.data_ptr(), pointer(z_bias), weight.data_ptr(), state.data_ptr(), batch.state_slots.data_ptr(), batch.q_start.data_ptr(),
+         out.data_ptr(), batch.n_seqs, int(heads), int(dim), int(value_dim), 1.0 / float(tau), float(q_scale), float(eps),
+         dtype_code(proj.dtype), dtype_code(weight.dtype), stream_handle())
+    return out
+
+
+_HEAD_INDEX = {}
+
+
+def head_linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """out[n, h, :] = weight[h] x[n, h, :] for ``x`` [N, H * K] and ``weight`` [H, R, K]: every head has a matrix of its
+    own.  Returns [N, H * R] in the activation type.  Steps of many rows in bfloat16 go to the library's batched product;
+    the others, and the 32-bit path, multiply row by row with sums whose order depends on K alone."""
+    check(x, "x")
+    heads, rows, inner = weight.shape
+    check(weight, "per-head matrices", x.dtype, inner)
+    tokens = x.shape[0]
+    if x.shape[1] != heads * inner:
+        raise KernelError(f"x has {x.shape[1]} columns; {heads} heads of {inner} are {heads * inner}")
+    if x.dtype == torch.bfloat16 and tokens > HEAD_LINEAR_ROWS:
+        out = torch.empty((tokens, heads, rows), dtype=x.dtype, device=x.device)
+        torch.bmm(x.view(tokens, heads, inner).transpose(0, 1), weight.transpose(1, 2), out=out.transpose(0, 1))
+        return out.view(tokens, heads * rows)
+    key = (x.device, tokens, heads)
+    index = _HEAD_INDEX.get(key)
+    if index is None:
+        index = (torch.arange(tokens * heads, dtype=torch.int32, device=x.device) % heads).contiguous()
+        _HEAD_INDEX[key] = index
+    return indexed_linear(x.view(tokens * heads, inner), weight, index, tokens * heads).view(tokens, heads * rows)
+
+
+HEAD_LINEAR_ROWS = 32     # up to this many tokens a bfloat16 step multiplies row by row
 
 
 def moe_route(x: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], top: int, scale: float,
@@ -546,14 +693,17 @@ def qkv_projection(x, weight: torch.Tensor, q_weight: Optional[torch.Tensor], k_
 
 def attention(qkv: torch.Tensor, batch, block_tables: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
               n_q_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int = 0,
-              value_dim: Optional[int] = None, sinks: Optional[torch.Tensor] = None, precise: bool = False) -> torch.Tensor:
+              value_dim: Optional[int] = None, sinks: Optional[torch.Tensor] = None, precise: bool = False,
+              q_stride: Optional[int] = None) -> torch.Tensor:
     """Attention of a step's tokens over the paged cache; ``qkv`` is the packed projection whose Q
-    heads have been normalised and rotated in place.  Chooses the kernel by dtype, head size and the
+    heads have been normalised and rotated in place (``q_stride``: elements from one token's queries to the next's,
+    where they are not such a packed row).  Chooses the kernel by dtype, head size and the
     shape of the batch; every choice computes the same function.  ``value_dim`` (default: head_dim) and ``sinks`` as
     in ``attention_generic``.  ``precise``: the attention weights may not be rounded to bfloat16 on their way into the
     P V product (the tensor-core kernels then carry each as two bfloat16 numbers)."""
     value_dim = head_dim if value_dim is None else int(value_dim)
-    q_stride = (n_q_heads + n_kv_heads) * head_dim + n_kv_heads * value_dim
+    if q_stride is None:
+        q_stride = (n_q_heads + n_kv_heads) * head_dim + n_kv_heads * value_dim
     if qkv.dtype == torch.bfloat16:
         from . import attention_bf16
         if value_dim == head_dim and sinks is None and not precise:

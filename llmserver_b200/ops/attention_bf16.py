@@ -245,3 +245,10 @@ def try_attention_precise(qkv, q_stride, batch, block_tables, k_pages, v_pages, 
          0 if partial_out is None else partial_out.data_ptr(), 0 if partial_ml is None else partial_ml.data_ptr(),
          wait_error_flag(qkv.device).data_ptr(), stream_handle())
     return out
+
+
+def try_attention_diff(qkv, gate_column, batch, block_tables, k_pages, v_pages, n_q_heads, n_kv_heads, dim, value_dim, scale,
+                       cap, window, lam, eps, out_scale, out) -> bool:
+    """Differential attention on the tensor cores where a tiled kernel takes the sizes; False when none does (the caller
+    then runs the kernel that takes every size)."""
+    return False

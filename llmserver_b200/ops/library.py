@@ -16,7 +16,7 @@ _P, _I, _F, _S = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 
 # name -> argument types (every launcher returns an int status; the stream comes last)
 SIGNATURES = {
-    "llm_embedding_gather": [_P, _P, _P, _I, _I, _I, _I, _S],
+    "llm_embedding_gather": [_P, _P, _P, _I, _I, _I, _I, _F, _S],
     "llm_add_rmsnorm": [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I, _P, _S],
     "llm_rmsnorm": [_P, _P, _P, _I, _I, _F, _I, _I, _S],
     "llm_silu_mul": [_P, _P, _I, _I, _I, _I, _S],
@@ -25,7 +25,11 @@ SIGNATURES = {
     "llm_qk_norm_rope_kv_write": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _I, _I, _I, _S],
     "llm_attention_generic": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _I, _S],
     "llm_rope_kv_write_split": [_P, _P, _F, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _I, _S],
-    "llm_normed_add_rmsnorm": [_P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I, _S],
+    "llm_normed_add_rmsnorm": [_P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I, _P, _S],
+    "llm_norm_rope_units": [_P, _I, _P, _P, _P, _F, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _I, _S],
+    "llm_attention_diff": [_P, _I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _F, _F, _F, _P, _I, _S],
+    "llm_gla_supports": [_I, _I],
+    "llm_gla_recurrent": [_P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _F, _F, _I, _I, _S],
     "llm_moe_route": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _S],
     "llm_moe_select": [_P, _P, _P, _P, _I, _I, _I, _F, _S],
     "llm_indexed_linear": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _S],

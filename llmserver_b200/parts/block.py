@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 from .base import Block
-from .norm import NormedDelta
+from .norm import NormedDelta, add_and_read
 from .registry import BLOCKS
 
 
@@ -69,3 +69,34 @@ class SandwichNormBlock(Block):
             return residual, pending
         out = self.feed_forward.forward(self.feed_forward_norm.add_norm(residual, pending))
         return residual, NormedDelta(out, self.feed_forward_out_norm)
+
+
+@BLOCKS.register("output_norm")
+class OutputNormBlock(Block):
+    """A norm on each sub-layer's output only; the sub-layers read the stream as it is:
+
+        h += mixer_out_norm(mixer(h));  h += feed_forward_out_norm(feed_forward(h))
+
+    A sub-layer's output travels on as a ``NormedDelta``: the kernel that hands the next sub-layer its input normalises
+    it, adds it to the 32-bit stream and returns the updated stream in the activation type (the model's final norm does
+    the same for the last layer, followed by its own normalisation).  A mixer that says ``output_bias`` has the bias of
+    its last projection added by that kernel, in 32-bit.  Parameters: ``feed_forward`` (default True; False: the layer
+    is its mixer alone) and the tensor-name prefixes of its parts."""
+
+    KNOWN_PARAMS = ("feed_forward", "mixer_prefix", "feed_forward_prefix", "mixer_out_norm_prefix", "feed_forward_out_norm_prefix")
+
+    @classmethod
+    def roles(cls, params):
+        roles = {"mixer": "mixer", "mixer_out_norm": "norm"}
+        if params.get("feed_forward", True):
+            roles.update({"feed_forward": "feed_forward", "feed_forward_out_norm": "norm"})
+        return roles
+
+    def forward(self, residual, delta, batch, cache):
+        act = self.mixer.runtime.dtype
+        mixed = self.mixer.forward(add_and_read(residual, delta, act), batch, cache)
+        pending = NormedDelta(mixed, self.mixer_out_norm, bias=getattr(self.mixer, "output_bias", None))
+        if not self.params.get("feed_forward", True):
+            return residual, pending
+        out = self.feed_forward.forward(add_and_read(residual, pending, act))
+        return residual, NormedDelta(out, self.feed_forward_out_norm, bias=getattr(self.feed_forward, "output_bias", None))

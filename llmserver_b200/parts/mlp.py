@@ -52,3 +52,38 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, sink=None):
         return ops.linear(ops.gate_up_silu(x, self.gate_up, self.group), self.down, sink=sink)
+
+
+@FEED_FORWARDS.register("clamped_glu")
+class ClampedGLU(FeedForward):
+    """A dense gated feed-forward whose gate and up values are clamped:
+
+        g = min(W_gate x, limit),  u = clamp(W_up x, -limit, limit),  y = W_down (g * sigmoid(alpha * g) * (u + 1))
+
+    the form the experts of ``routed_experts`` have, as one dense layer.  Parameters: ``hidden``, ``intermediate``,
+    ``limit``; ``alpha`` (default 1.702); ``names``: pairs (role, tensor name behind the prefix) for the roles gate, up
+    and down.  gate and up are one [2 I, H] matrix, gate rows first; the activation is formed in 32-bit."""
+
+    KNOWN_PARAMS = ("hidden", "intermediate", "limit", "alpha", "names")
+    NAMES = {"gate": "gate", "up": "up", "down": "down"}
+
+    @classmethod
+    def names(cls, params) -> dict:
+        return {**cls.NAMES, **dict(params.get("names") or ())}
+
+    @classmethod
+    def declare_weights(cls, params):
+        hidden, intermediate = int(params["hidden"]), int(params["intermediate"])
+        name = cls.names(params)
+        return {name["gate"]: WeightDecl((intermediate, hidden)), name["up"]: WeightDecl((intermediate, hidden)),
+                name["down"]: WeightDecl((hidden, intermediate))}
+
+    def __init__(self, params, weights, runtime):
+        super().__init__(params, weights, runtime)
+        name = self.names(params)
+        self.gate_up = torch.cat([weights[name["gate"]], weights[name["up"]]], dim=0).contiguous()
+        self.down = weights[name["down"]].contiguous()
+        self.limit, self.alpha = float(params["limit"]), float(params.get("alpha", 1.702))
+
+    def forward(self, x):
+        return ops.linear(ops.clamped_glu(ops.linear(x, self.gate_up), self.limit, self.alpha), self.down)

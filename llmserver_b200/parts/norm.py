@@ -16,10 +16,24 @@ from .registry import NORMS
 class NormedDelta:
     """A sub-layer's output that still has to pass a norm of its own before it joins the stream: the block hands this
     to the next norm's ``add_norm`` in place of a plain delta, and one kernel normalises it, adds it (with ``extra``,
-    a second 32-bit stream, when given) and normalises the stream for the next sub-layer."""
+    a second 32-bit stream, when given) and normalises the stream for the next sub-layer.  ``bias``: the bias of the
+    projection that made ``delta`` (float32 [width]), which that kernel adds in 32-bit before it normalises."""
     delta: Optional[torch.Tensor]
     norm: Optional["RMSNorm"] = None
     extra: Optional[torch.Tensor] = None
+    bias: Optional[torch.Tensor] = None
+
+
+def add_and_read(residual: torch.Tensor, delta, act_dtype: torch.dtype) -> torch.Tensor:
+    """Adds what is pending (a ``NormedDelta`` or nothing) to the 32-bit stream and returns the stream itself in the
+    activation type: the input of a sub-layer that reads the stream without a norm in front."""
+    if delta is None:
+        return ops.normed_add_rmsnorm(residual, None, None, 0.0, None, 0.0, act_dtype=act_dtype)
+    if not isinstance(delta, NormedDelta):
+        raise TypeError(f"a block that reads the stream as it is takes a NormedDelta or nothing, not {type(delta).__name__}")
+    post = delta.norm
+    return ops.normed_add_rmsnorm(residual, delta.delta, post.weight, post.eps, None, 0.0, extra=delta.extra,
+                                  act_dtype=act_dtype, delta_bias=delta.bias)
 
 
 @NORMS.register("rmsnorm")
@@ -45,7 +59,7 @@ class RMSNorm(Norm):
             post = delta.norm
             return ops.normed_add_rmsnorm(residual, delta.delta, post.weight if post is not None else None,
                                           post.eps if post is not None else 0.0, self.weight, self.eps,
-                                          extra=delta.extra, rows=rows, act_dtype=self.runtime.dtype)
+                                          extra=delta.extra, rows=rows, act_dtype=self.runtime.dtype, delta_bias=delta.bias)
         if isinstance(delta, ops.StreamSink):
             # the part in front added its result to the stream itself and, if asked, prepared this norm's input
             if delta.owner is not self or not delta.added:

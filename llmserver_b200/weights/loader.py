@@ -25,6 +25,11 @@ _FLOAT_FAMILY = {"F64", "F32", "F16", "BF16"}
 _INT_FAMILY = {"I64", "I32", "I16", "I8", "U8"}
 
 
+def shape_fits(shape, declared) -> bool:
+    """A declared dimension of -1 takes any size (a rank that only the tensor's shape gives)."""
+    return len(shape) == len(declared) and all(want in (-1, have) for have, want in zip(shape, declared))
+
+
 def check_checkpoint(reader: CheckpointReader, wanted: Dict[str, WeightDecl], optional=()) -> None:
     missing, unexpected, wrong = [], [], []
     present = set(reader.names())
@@ -33,7 +38,7 @@ def check_checkpoint(reader: CheckpointReader, wanted: Dict[str, WeightDecl], op
             missing.append(name)
             continue
         shape, dtype = reader.shape_and_dtype(name)
-        if tuple(shape) != tuple(declaration.shape):
+        if not shape_fits(shape, declaration.shape):
             wrong.append(f"{name}: shape {list(shape)} where {list(declaration.shape)} is expected")
         family = _INT_FAMILY if declaration.kind == TABLE else _FLOAT_FAMILY
         if dtype.upper() not in family:

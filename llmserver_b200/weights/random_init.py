@@ -22,9 +22,14 @@ def _tensor_seed(seed: int, name: str) -> int:
     return int.from_bytes(digest[:8], "little") & 0x7FFFFFFFFFFFFFFF
 
 
+FREE_DIMENSION = 16     # size given to a dimension that a declaration leaves open (-1)
+
+
 def random_tensor(name: str, declaration: WeightDecl, seed: int, device="cpu") -> torch.Tensor:
     """float32 values (int32 for tables) on ``device``; CPU and CUDA generators give different
     streams, so a model made on one device is not reproduced on the other."""
+    if -1 in declaration.shape:
+        declaration = WeightDecl(tuple(FREE_DIMENSION if size == -1 else size for size in declaration.shape), declaration.kind)
     generator = torch.Generator(device=device)
     generator.manual_seed(_tensor_seed(seed, name))
     if declaration.kind == TABLE:
@@ -67,7 +72,7 @@ def write_model_folder(config, folder: str, seed: int, dtype: torch.dtype = torc
     with open(os.path.join(folder, "config.json"), "w") as handle:
         json.dump(raw, handle, indent=2)
     wanted = declared_weights(spec)
-    sizes = {name: int(torch.tensor(declaration.shape).prod()) * (4 if declaration.kind == TABLE else torch.empty(0, dtype=dtype).element_size())
+    sizes = {name: abs(int(torch.tensor(declaration.shape).prod())) * (FREE_DIMENSION if -1 in declaration.shape else 1) * (4 if declaration.kind == TABLE else torch.empty(0, dtype=dtype).element_size())
              for name, declaration in wanted.items()}
     shards, current, held = [], [], 0
     for name in wanted:
