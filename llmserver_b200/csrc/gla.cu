@@ -5,7 +5,8 @@
 //     S_t[i][j]  = alpha_t[i] * S_(t-1)[i][j] + k_t[i] * v_t[j]
 //     o_t[j]     = sum_i S_t[i][j] * q_t[i] * q_scale
 //     out_t[j]   = o_t[j] / sqrt(mean_j(o_t^2) + eps) * weight[j] * silu(g_t[j])
-// q, k, v and g are column ranges of one packed projection row; z is a projection of its own.  The state of a
+// q, k, v and g are column ranges of one packed projection row; z is a projection of its own, kept in 32-bit (the
+// decay is the one quantity here whose error compounds from token to token).  The state of a
 // sequence lives in its slot of `state` [slots, heads, dim, vdim] (float32): it is read when the block starts on the
 // sequence's tokens of this step and written back behind the last of them, so a prompt may arrive in portions of any
 // size and single decoded tokens continue it.  A slot that a new request takes over is zeroed by the cache manager.
@@ -23,7 +24,7 @@
 struct GlaArgs {
     const void* proj;       // [N, row_width]
     int row_width, q_offset, k_offset, v_offset, g_offset;
-    const void* z;          // [N, heads * dim]
+    const float* z;         // [N, heads * dim], 32-bit in either path
     const float* z_bias;    // [heads * dim] or null
     const void* weight;     // [vdim] norm weight
     float* state;           // [slots, heads, dim, vdim]
@@ -53,7 +54,7 @@ __global__ void __launch_bounds__(R == 128 ? 256 : 512) gla_recurrent_kernel(Gla
     const int row0 = partition * R;
     const bool owner = column < vdim && partition < a.partitions;
     const T* proj = (const T*)a.proj;
-    const T* z = (const T*)a.z;
+    const float* z = a.z;
 
     float S[R];
     float* state = a.state + ((size_t)a.state_slots[seq] * a.heads + head) * dim * vdim;
@@ -70,7 +71,7 @@ __global__ void __launch_bounds__(R == 128 ? 256 : 512) gla_recurrent_kernel(Gla
                 const T* row = proj + (size_t)(first + t) * a.row_width;
                 qv = Num<T>::load(row + a.q_offset + head * dim + i) * a.q_scale;
                 kv = Num<T>::load(row + a.k_offset + head * dim + i);
-                float zz = Num<T>::load(z + (size_t)(first + t) * a.heads * dim + head * dim + i);
+                float zz = z[(size_t)(first + t) * a.heads * dim + head * dim + i];
                 if (a.z_bias) zz += a.z_bias[head * dim + i];
                 // log sigmoid(zz) = -softplus(-zz), stable on both sides
                 const float log_sigmoid = zz >= 0.0f ? -log1pf(expf(-zz)) : zz - log1pf(expf(zz));
@@ -151,7 +152,7 @@ LLM_EXPORT int llm_gla_supports(int dim, int vdim) {
 }
 
 LLM_EXPORT int llm_gla_recurrent(const void* proj, int row_width, int q_offset, int k_offset, int v_offset, int g_offset,
-                                 const void* z, const float* z_bias, const void* weight, float* state, const int* state_slots,
+                                 const float* z, const float* z_bias, const void* weight, float* state, const int* state_slots,
                                  const int* q_start, void* out, int n_seqs, int heads, int dim, int vdim, float inverse_tau,
                                  float q_scale, float eps, int dtype, int weight_dtype, cudaStream_t stream) {
     if (n_seqs == 0) return LLM_OK;

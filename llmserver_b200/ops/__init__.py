@@ -394,10 +394,10 @@ def gla_recurrent(proj: torch.Tensor, q_column: int, k_column: int, v_column: in
         out   = o / sqrt(mean(o^2) + eps) * weight * silu(g)          per head, over value_dim
 
     q, k (heads * dim columns each), v and g (heads * value_dim) start at the given columns of ``proj``; ``z`` is
-    [N, heads * dim].  Returns [N, heads * value_dim] in the activation type; the recurrence itself is 32-bit."""
+    float32 [N, heads * dim] in either path.  Returns [N, heads * value_dim] in the activation type; the recurrence itself is 32-bit."""
     check(proj, "packed projection")
     tokens, row_width = proj.shape
-    check(z, "decay projection", proj.dtype, heads * dim)
+    check(z, "decay projection", torch.float32, heads * dim)
     if z_bias is not None:
         check(z_bias, "decay bias", torch.float32, heads * dim)
     check(weight, "norm weight", last_dim=value_dim)

@@ -87,6 +87,9 @@ class DifferentialAttention(Mixer):
         if params.get("gate", True):
             self.gate_column = self.qkv_columns
             rows.append(weights[name["g"]])
+        total = sum(int(w.shape[0]) for w in rows)
+        if total % 8:       # rows of the packed projection keep their 16-byte alignment
+            rows.append(torch.zeros((8 - total % 8, rows[0].shape[1]), dtype=rows[0].dtype, device=rows[0].device))
         self.fused = torch.cat(rows, dim=0).contiguous()
         self.out = weights[name["o"]].contiguous()
         self.bias = self.output_bias = None

@@ -20,8 +20,8 @@ class GatedLinearAttention(Mixer):
         S_t = diag(alpha_t) S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t
         y = W_o (concat_h(rmsnorm(o_h) * w) * silu(W_g x))                   w of value_dim, shared by the heads
 
-    The state is float32 [heads, dim, value_dim] in the request's state slot; the decay, from the bias on, and the
-    recurrence are 32-bit in either path; the projections run in the activation type.  Parameters: ``hidden``,
+    The state is float32 [heads, dim, value_dim] in the request's state slot; the decay (from the 32-bit sums of its
+    second projection on) and the recurrence are 32-bit in either path; the other projections run in the activation type.  Parameters: ``hidden``,
     ``heads``, ``dim``, ``value_dim``, ``tau``, ``decay_rank`` (rows of W_a1; None: the tensor's shape says), ``eps``; ``names``: pairs (role, tensor
     name behind the prefix) for q, k, v, g, o, norm, a1, a2 (the bias is a2's name with ".b" added)."""
 
@@ -74,7 +74,7 @@ class GatedLinearAttention(Mixer):
 
     def forward(self, x, batch, cache):
         proj = ops.linear(x, self.fused)
-        z = ops.linear(ops.linear(x, self.decay_in), self.decay_out)
+        z = ops.linear_wide(ops.linear(x, self.decay_in), self.decay_out)      # 32-bit sums, never rounded to the activation type
         q_column, k_column, v_column, g_column = self.columns
         mixed = ops.gla_recurrent(proj, q_column, k_column, v_column, g_column, z, self.decay_bias, self.norm, cache.state,
                                   batch, self.heads, self.dim, self.value_dim, self.tau, self.dim ** -0.5, self.eps)
