@@ -84,8 +84,12 @@ class CacheGroup:
 
 
 class StateSlots:
+    """Slots 0 .. num_slots - 1 go to requests; the storage has one more, ``null_slot``, that belongs to nobody: rows
+    that only pad a batch to a fixed size read and write their state there."""
+
     def __init__(self, num_slots: int):
         self.num_slots = num_slots
+        self.null_slot = num_slots
         self.free: List[int] = list(range(num_slots - 1, -1, -1))
         self.slot_of: Dict[object, int] = {}
         self.storage: Dict[int, object] = {}    # schedule entry -> tensor [num_slots, *shape]
@@ -167,7 +171,7 @@ class CacheManager:
                 group.key_storage = torch.zeros(shape + (need.head_dim,), dtype=dtype, device=device)
                 group.value_storage = torch.zeros(shape + (int(need.value_dim),), dtype=dtype, device=device)
         for entry, need in self.state_entries.items():
-            self.slots.storage[entry] = torch.zeros((self.slots.num_slots,) + tuple(need.shape),
+            self.slots.storage[entry] = torch.zeros((self.slots.num_slots + 1,) + tuple(need.shape),
                                                     dtype=getattr(torch, need.dtype), device=device)
 
     def pages_of_entry(self, entry: int):

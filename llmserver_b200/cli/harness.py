@@ -351,3 +351,95 @@ def dense_step_cost(size: dict, layers: int, tokens: int, cached_tokens: float, 
     weights = (heads + 2 * kv_heads) * dim * width + width * heads * dim + 3 * width * inter
     return (2 * layers * weights + 2 * layers * kv_heads * 2 * dim * cached_tokens + COMPARE_VOCAB * width * 2,
             2 * tokens * layers * weights + 2 * layers * heads * 2 * dim * pairs)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Dikusun beside the dense decoder at equal size
+# ---------------------------------------------------------------------------------------------------------------------
+def _dikusun_size(width, ff, attention, latent, gla, kinds):
+    return dict(width=width, ff=ff, attention=attention, latent=latent, gla=gla, kinds=kinds)
+
+
+def _dikusun_mixers(width, heads, kv_heads):
+    """Mixers of one width: differential attention whose two maps together are as wide as a dense head, a window of
+    1024 tokens; latent attention with a latent of 128 (the widest head the tensor-core attention kernels take);
+    gated linear attention with keys half and values as wide as the stream."""
+    return (dict(heads=heads, kv_heads=kv_heads, dim=64, vdim=128, scale=0.125, diff=0.3, softcap=50.0, mask={"size": 1024},
+                 rot={"base": 1000000.0, "dims": 64}),
+            dict(heads=16, dim=128, vdim=128, q_rank=width // 4, kv_rank=128, scale=128 ** -0.5),
+            dict(heads=width // 128, dim=64, vdim=128, tau=16.0, a_rank=16))
+
+
+# Layer sizes that resemble served models, each as four layers of one kind of mixer and as a mix of the three; every
+# layer has a feed-forward three times as wide as the stream.
+DIKUSUN_SIZES = {}
+for _width, _heads, _kv in ((2048, 16, 4), (4096, 32, 8)):
+    _a, _l, _g = _dikusun_mixers(_width, _heads, _kv)
+    for _label, _kinds in (("attention", ("attention",) * 4), ("latent", ("latent_attention",) * 4), ("gla", ("gla",) * 4),
+                           ("mixed", ("attention", "gla", "latent_attention", "attention"))):
+        DIKUSUN_SIZES[f"w{_width}-{_label}"] = _dikusun_size(_width, 3 * _width, _a, _l, _g, _kinds)
+
+
+def dikusun_config(size: dict, layers: int = None):
+    from llmserver_b200.config import DikusunConfig
+    mixer_of = {"attention": size["attention"], "latent_attention": size["latent"], "gla": size["gla"]}
+    kinds = size["kinds"] if layers is None else [size["kinds"][index % len(size["kinds"])] for index in range(layers)]
+    return DikusunConfig.from_dict({"architecture": "Dikusun", "vocab": COMPARE_VOCAB, "width": size["width"], "norm": {"eps": 1e-6},
+                                    "embedding": {"scale": 1.0},
+                                    "layers": [{"type": kind, "mixer": mixer_of[kind], "mlp": {"kind": "dense", "ff": size["ff"], "limit": 7.0}}
+                                               for kind in kinds]})
+
+
+def dikusun_dense_twin(size: dict, layers: int):
+    """The dense decoder of equal size: the same width, the attention layers' head count with heads of 128, the same
+    feed-forward."""
+    from llmserver_b200.config import Qwen3Config
+    raw = dict(_qwen3(layers, size["width"], size["attention"]["heads"], size["ff"]),
+               num_key_value_heads=size["attention"]["kv_heads"], head_dim=128, vocab_size=COMPARE_VOCAB)
+    return Qwen3Config.from_dict(raw)
+
+
+def dikusun_step_cost(size: dict, layers: int, tokens: int, sequences: int, context: float):
+    """(bytes, FLOPs) of one step in which each of ``sequences`` requests brings tokens / sequences new tokens behind
+    ``context`` cached ones: bytes = every weight once + what the mixers read of cache and state; FLOPs = the products
+    of the tokens + what the mixers do per (query, key) pair or per token of a recurrence."""
+    width, ff = size["width"], size["ff"]
+    per_sequence = tokens / sequences
+    total_bytes = COMPARE_VOCAB * width * 2.0
+    flops = 0.0
+    kinds = [size["kinds"][index % len(size["kinds"])] for index in range(layers)]
+    for kind in kinds:
+        weights = 3.0 * width * ff
+        if kind == "attention":
+            m = size["attention"]
+            heads, kv, dim, vdim, window = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["mask"]["size"]
+            weights += (heads * 2 * dim + kv * 2 * dim + kv * vdim + heads) * width + width * heads * vdim
+            seen = min(context + per_sequence, window)
+            total_bytes += sequences * seen * kv * (2 * dim + vdim) * 2.0
+            pairs = sequences * sum(min(context + i + 1, window) for i in range(int(per_sequence)))
+            flops += 2.0 * heads * (2 * dim + 2 * vdim) * pairs
+        elif kind == "latent_attention":
+            m = size["latent"]
+            heads, dim, vdim, q_rank, kv_rank = m["heads"], m["dim"], m["vdim"], m["q_rank"], m["kv_rank"]
+            weights += (q_rank + kv_rank) * width + heads * dim * (q_rank + kv_rank) + heads * vdim * kv_rank + width * heads * vdim
+            total_bytes += sequences * (context + per_sequence) * kv_rank * 2.0
+            pairs = sequences * (per_sequence * context + per_sequence * (per_sequence + 1) / 2)
+            flops += 2.0 * heads * 2 * kv_rank * pairs
+        else:
+            m = size["gla"]
+            heads, dim, vdim, rank = m["heads"], m["dim"], m["vdim"], m["a_rank"]
+            weights += (2 * heads * dim + 2 * heads * vdim + rank) * width + heads * dim * rank + width * heads * vdim
+            total_bytes += sequences * heads * dim * vdim * 4.0 * 2          # the state, read and written
+            flops += tokens * heads * dim * vdim * 5.0
+        total_bytes += 2.0 * weights
+        flops += 2.0 * tokens * weights
+    return total_bytes, flops
+
+
+def dikusun_dense_cost(size: dict, layers: int, tokens: int, sequences: int, context: float):
+    width, heads, kv, dim, inter = size["width"], size["attention"]["heads"], size["attention"]["kv_heads"], 128, size["ff"]
+    weights = (heads + 2 * kv) * dim * width + width * heads * dim + 3 * width * inter
+    per_sequence = tokens / sequences
+    pairs = sequences * (per_sequence * context + per_sequence * (per_sequence + 1) / 2)
+    return (2.0 * layers * weights + 2.0 * layers * kv * 2 * dim * sequences * (context + per_sequence) + COMPARE_VOCAB * width * 2.0,
+            2.0 * tokens * layers * weights + 2.0 * layers * heads * 2 * dim * pairs)

@@ -128,7 +128,7 @@ __device__ __forceinline__ float gated_activation(float gate, float up, float li
 // One warp per (pair, output element).  `rows` output elements per pair; the gated form reads row r and row rows + r.
 template <typename T, typename O, bool GATED>
 __global__ void indexed_linear_kernel(const T* __restrict__ in, const T* __restrict__ weight, const int* __restrict__ index,
-                                      O* __restrict__ out, int rows, int inner, int in_div, float limit, float alpha) {
+                                      O* __restrict__ out, int rows, int inner, int in_div, float limit, float alpha, int index_mod) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float in_row[];       // [inner]
@@ -136,7 +136,7 @@ __global__ void indexed_linear_kernel(const T* __restrict__ in, const T* __restr
     const T* src = in + (size_t)(pair / in_div) * inner;
     for (int i = threadIdx.x; i < inner; i += blockDim.x) in_row[i] = Num<T>::load(src + i);
     __syncthreads();
-    const int expert = index ? index[pair] : 0;
+    const int expert = index ? index[pair] : (index_mod > 0 ? pair % index_mod : 0);     // no index: pair p uses matrix p mod index_mod
     const T* matrix = weight + (size_t)expert * (GATED ? 2 : 1) * rows * inner;
     // four consecutive output elements per warp, worked on together so that their loads are in flight at the same time;
     // each element's sum runs over k in an order that depends on the inner size alone
@@ -258,7 +258,7 @@ LLM_EXPORT int llm_moe_select(const float* logits, const float* correction, int*
 
 LLM_EXPORT int llm_indexed_linear(const void* in, const void* weight, const int* index, void* out, int n_pairs, int rows,
                                   int inner, int in_div, int gated, float limit, float alpha, int dtype, int out_f32,
-                                  cudaStream_t stream) {
+                                  int index_mod, cudaStream_t stream) {
     if (n_pairs == 0 || rows == 0) return LLM_OK;
     if (in_div <= 0 || inner <= 0) {
         llm_set_error("indexed_linear: in_div %d and inner %d must be positive", in_div, inner);
@@ -282,7 +282,7 @@ LLM_EXPORT int llm_indexed_linear(const void* in, const void* weight, const int*
             if (status != LLM_OK) return status;                                                                        \
         }                                                                                                               \
         llm_launch(indexed_linear_kernel<T, O, GATED>, grid, warps * 32, shared, stream, (const T*)in, (const T*)weight, index, \
-                   (O*)out, rows, inner, in_div, limit, alpha);                                                         \
+                   (O*)out, rows, inner, in_div, limit, alpha, index_mod);                                                       \
     } while (0)
     LLM_DISPATCH_DTYPE(dtype, {
         if (gated && out_f32) {

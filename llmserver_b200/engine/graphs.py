@@ -42,11 +42,11 @@ class DecodeRows:
     what a decode step changes is rewritten (``_update``); anything else repacks the whole buffer."""
 
     def __init__(self, batch_size: int, n_groups: int, table_width: int, vocab_size: int, null_pages: Sequence[int],
-                 host_view: Optional[np.ndarray] = None):
+                 host_view: Optional[np.ndarray] = None, null_slot: int = 0):
         self.batch_size, self.vocab_size = batch_size, vocab_size
         self.layout = BatchLayout(batch_size, batch_size, batch_size, (table_width,) * n_groups)
         self.host_view = np.zeros(self.layout.total, dtype=np.int32) if host_view is None else host_view
-        self.pad = SequenceSlice(None, [0], 0, [0], [[page] for page in null_pages], 0)
+        self.pad = SequenceSlice(None, [0], 0, [0], [[page] for page in null_pages], null_slot)
         self.row_tables: Optional[List[Sequence[Sequence[int]]]] = None
         self.table_lengths: Optional[List[List[int]]] = None
         self.repacks = 0
@@ -96,6 +96,8 @@ class DecodeRows:
         host[off["token_ids"]:off["token_ids"] + count] = tokens
         host[off["positions"]:off["positions"] + count] = starts
         host[off["context_len"]:off["context_len"] + count] = starts + 1
+        # a model without paged groups has no tables by which to recognise its rows: their state slots are rewritten
+        host[off["state_slots"]:off["state_slots"] + count] = np.fromiter((piece.state_slot for piece in slices), dtype=np.int32, count=count)
         host[off["temperatures"]:off["temperatures"] + count] = np.fromiter(
             (row.temperature for row in sampling), dtype=np.float32, count=count).view(np.int32)
         host[off["seeds"]:off["seeds"] + 2 * count] = np.fromiter(
@@ -121,12 +123,12 @@ class DecodeGraph:
     (utils/cuda_graph.py:11-99)."""
 
     def __init__(self, model, batch_size: int, n_groups: int, table_width: int, max_context: int, vocab_size: int,
-                 null_pages: Sequence[int]):
+                 null_pages: Sequence[int], null_slot: int = 0):
         self.model, self.vocab_size, self.batch_size = model, vocab_size, batch_size
         device = model.runtime.device
         layout = BatchLayout(batch_size, batch_size, batch_size, (table_width,) * n_groups)
         self.host = torch.zeros(layout.total, dtype=torch.int32, pin_memory=True)
-        self.rows = DecodeRows(batch_size, n_groups, table_width, vocab_size, null_pages, self.host.numpy())
+        self.rows = DecodeRows(batch_size, n_groups, table_width, vocab_size, null_pages, self.host.numpy(), null_slot)
         self.layout = self.rows.layout
         self.buffer = torch.zeros(self.layout.total, dtype=torch.int32, device=device)
         # the static batch claims the longest context, so that launch shapes cover every later step
@@ -168,10 +170,10 @@ class DecodeGraphs:
         self.table_width = -(-max_context // cache.page_size)
         self.graphs: Dict[int, DecodeGraph] = {}
         self.seen: Dict[int, int] = {}
-        # every mixer has to say that it can be captured; and rows that only pad a batch would have to own a state
-        # slot, which the slot allocator does not set aside
+        # every mixer has to say that it can be captured; rows that only pad a batch keep their state in the slot
+        # that the cache manager sets aside for them
         mixers = [getattr(layer, "mixer", None) for layer in getattr(model, "layers", [])]
-        self.failed = bool(cache.state_entries) or any(not getattr(mixer, "capturable", True) for mixer in mixers)
+        self.failed = any(not getattr(mixer, "capturable", True) for mixer in mixers)
         self.null_pages = None
 
     def forget_rows(self) -> None:
@@ -211,4 +213,4 @@ class DecodeGraphs:
     def capture(self, size: int):
         """Makes the replayable step for ``size`` rows (tests without a GPU put a host-side stand-in here)."""
         return DecodeGraph(self.model, size, len(self.cache.groups), self.table_width, self.max_context,
-                           self.model.spec.vocab_size, self.null_pages)
+                           self.model.spec.vocab_size, self.null_pages, self.cache.slots.null_slot)

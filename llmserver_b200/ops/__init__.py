@@ -415,9 +415,6 @@ def gla_recurrent(proj: torch.Tensor, q_column: int, k_column: int, v_column: in
     return out
 
 
-_HEAD_INDEX = {}
-
-
 def head_linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """out[n, h, :] = weight[h] x[n, h, :] for ``x`` [N, H * K] and ``weight`` [H, R, K]: every head has a matrix of its
     own.  Returns [N, H * R] in the activation type.  Steps of many rows in bfloat16 go to the library's batched product;
@@ -432,12 +429,7 @@ def head_linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
         out = torch.empty((tokens, heads, rows), dtype=x.dtype, device=x.device)
         torch.bmm(x.view(tokens, heads, inner).transpose(0, 1), weight.transpose(1, 2), out=out.transpose(0, 1))
         return out.view(tokens, heads * rows)
-    key = (x.device, tokens, heads)
-    index = _HEAD_INDEX.get(key)
-    if index is None:
-        index = (torch.arange(tokens * heads, dtype=torch.int32, device=x.device) % heads).contiguous()
-        _HEAD_INDEX[key] = index
-    return indexed_linear(x.view(tokens * heads, inner), weight, index, tokens * heads).view(tokens, heads * rows)
+    return indexed_linear(x.view(tokens * heads, inner), weight, None, tokens * heads, cyclic=True).view(tokens, heads * rows)
 
 
 HEAD_LINEAR_ROWS = 32     # up to this many tokens a bfloat16 step multiplies row by row
@@ -477,8 +469,9 @@ def moe_select(logits: torch.Tensor, correction: Optional[torch.Tensor], top: in
 
 
 def indexed_linear(x: torch.Tensor, weight: torch.Tensor, index: Optional[torch.Tensor], pairs: int, in_div: int = 1,
-                   gated: Optional[tuple] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """out[p] = weight[index[p]] x[p // in_div] for p < ``pairs``; ``weight`` is [E, R, K] (``index`` None: E = 1).
+                   gated: Optional[tuple] = None, out_dtype: Optional[torch.dtype] = None, cyclic: bool = False) -> torch.Tensor:
+    """out[p] = weight[index[p]] x[p // in_div] for p < ``pairs``; ``weight`` is [E, R, K] (``index`` None: E = 1, or,
+    ``cyclic``, pair p uses matrix p mod E).
     ``gated`` = (limit, alpha): the matrices hold R gate rows and then R up rows, [E, 2 R, K], and the result is
     min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + 1)."""
     check(x, "x")
@@ -490,7 +483,7 @@ def indexed_linear(x: torch.Tensor, weight: torch.Tensor, index: Optional[torch.
         check(index, "expert index", torch.int32)
         if index.numel() < pairs:
             raise KernelError(f"{index.numel()} expert indices for {pairs} pairs")
-    elif weight.shape[0] != 1:
+    elif weight.shape[0] != 1 and not cyclic:
         raise KernelError("without an index the weights hold one matrix")
     if x.shape[0] * in_div < pairs:
         raise KernelError(f"{x.shape[0]} input rows cannot serve {pairs} pairs, {in_div} per row")
@@ -501,7 +494,8 @@ def indexed_linear(x: torch.Tensor, weight: torch.Tensor, index: Optional[torch.
     limit, alpha = gated if gated else (0.0, 0.0)
     call("llm_indexed_linear", x.data_ptr(), weight.data_ptr(), pointer(index), out.data_ptr(), pairs, rows, x.shape[-1],
          int(in_div), int(bool(gated)), float(limit), float(alpha), dtype_code(x.dtype),
-         int(out_dtype == torch.float32 and x.dtype != torch.float32), stream_handle())
+         int(out_dtype == torch.float32 and x.dtype != torch.float32), weight.shape[0] if cyclic and index is None else 0,
+         stream_handle())
     return out
 
 

@@ -247,8 +247,22 @@ def try_attention_precise(qkv, q_stride, batch, block_tables, k_pages, v_pages, 
     return out
 
 
+DIFF_KERNEL = os.environ.get("LLMSERVER_B200_DIFF_ATTENTION", "mma")      # "generic": always the kernel that takes every size
+
+
 def try_attention_diff(qkv, gate_column, batch, block_tables, k_pages, v_pages, n_q_heads, n_kv_heads, dim, value_dim, scale,
                        cap, window, lam, eps, out_scale, out) -> bool:
-    """Differential attention on the tensor cores where a tiled kernel takes the sizes; False when none does (the caller
-    then runs the kernel that takes every size)."""
-    return False
+    """Differential attention on the tensor cores where the tiled kernel takes the sizes (units and values of 64 or 128,
+    rows of the packed projection 16-byte aligned); False when it does not (the caller then runs the kernel that takes
+    every size).  Prompt portions and single tokens go in one launch."""
+    row_width = qkv.shape[1]
+    if DIFF_KERNEL != "mma" or row_width % 8 or not library().llm_attention_diff_mma_supports(dim, value_dim, n_q_heads, n_kv_heads):
+        return False
+    check(qkv, "qkv", torch.bfloat16)
+    gate = 0 if gate_column is None else qkv.data_ptr() + gate_column * qkv.element_size()
+    call("llm_attention_diff_mma", qkv.data_ptr(), row_width, gate, row_width, k_pages.data_ptr(), v_pages.data_ptr(),
+         block_tables.data_ptr(), block_tables.shape[-1], batch.q_start.data_ptr(), batch.context_len.data_ptr(), out.data_ptr(),
+         batch.n_seqs, int(batch.max_q_len), n_q_heads, n_kv_heads, int(dim), int(value_dim), k_pages.shape[2], k_pages.shape[0],
+         float(scale), float(cap or 0.0), int(window or 0), float(lam), float(eps), float(out_scale),
+         wait_error_flag(qkv.device).data_ptr(), stream_handle())
+    return True

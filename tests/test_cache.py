@@ -69,7 +69,7 @@ def test_groups_follow_the_needs():
     assert cache.groups[0].storage.shape == (2, 2, 8, 2, 4, 16)
     k_pages, v_pages, group = cache.pages_of_entry(4)
     assert k_pages.shape == (8, 2, 4, 16) and group == 1
-    assert cache.state_of_entry(5).shape == (4, 3, 2)
+    assert cache.state_of_entry(5).shape == (4 + 1, 3, 2)      # one slot more than requests can hold: the padding rows' slot
 
 
 def test_ensure_allocates_all_or_nothing_and_free_gives_everything_back():

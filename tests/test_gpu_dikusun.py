@@ -296,9 +296,9 @@ def test_differential_attention_kernel(dtype, heads, kv_heads, dim, vdim, window
         batch = build_batch(slices, 1, DEVICE)
         q_cols = heads * 2 * dim
         for use_gate in (True, False):
-            packed = torch.zeros((len(queries), q_cols + 24 + heads), dtype=dtype)
+            packed = torch.zeros((len(queries), -(-(q_cols + 24 + heads) // 8) * 8), dtype=dtype)
             packed[:, :q_cols] = q.reshape(len(queries), q_cols)
-            packed[:, q_cols + 24:] = gate
+            packed[:, q_cols + 24:q_cols + 24 + heads] = gate
             want, maps = _differential_plain(q, gate, keys, values, queries, heads, kv_heads, scale, cap, window, lam, eps, out_scale, use_gate)
             out = ops.attention_diff(packed.to(DEVICE), q_cols + 24 if use_gate else None, batch, batch.block_tables[0],
                                      k_pages.to(DEVICE), v_pages.to(DEVICE), heads, kv_heads, dim, vdim, scale, cap, window, lam,
@@ -311,6 +311,56 @@ def test_differential_attention_kernel(dtype, heads, kv_heads, dim, vdim, window
                 assert float(p[spike[1] - first]) > 0.9      # the spiked key really carries the row of its map
             else:
                 assert float(p.max()) < 0.9                  # outside the window it is not there at all
+
+
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,window,cap", [(4, 2, 64, 64, 70, 40.0), (8, 1, 64, 128, 0, 0.0), (6, 2, 128, 128, 300, 50.0),
+                                                                (3, 3, 128, 64, 1000, 0.0), (32, 2, 64, 64, 17, 0.0)])
+def test_tiled_differential_attention_kernel(heads, kv_heads, dim, vdim, window, cap):
+    """The bfloat16 kernel on the tensor cores against the plain implementation and against the kernel that takes every
+    size: a whole prompt, a portion behind cached tokens, single decoded tokens of short contexts and of a long one, all
+    in one batch, and a batch of single tokens alone (the launch shape of a decode step); keys through shuffled pages
+    that do not align with the kernel's tiles.  One decoded query's score for the first key inside its window (or, with
+    no window, for a key far back) towers over the rest, so weights rounded to 8 bits would not pass either."""
+    from llmserver_b200 import ops
+    from llmserver_b200.engine.batch import SequenceSlice, build_batch
+    from llmserver_b200.ops import attention_bf16
+    from llmserver_b200.ops.library import check_wait_errors, launch_count
+    page_size = 16 if dim == 64 else 24
+    lengths = [300, 41, 1, 130, 2500]
+    lam, eps, out_scale, scale = 0.41, 1e-6, 0.8, 1.0 / math.sqrt(dim)
+    for new_tokens in ([1, 41, 1, 30, 1], [1, 1, 1, 1, 1]):
+        queries = [(s, p) for s, (length, count) in enumerate(zip(lengths, new_tokens)) for p in range(length - count, length)]
+        last_query = len(queries) - 1
+        inside = 2499 - window + 1 if window else 15
+        for spike in ((last_query, inside, 0), (last_query, inside, 1), (last_query, inside - 1, 1) if window else None, None):
+            q, gate, keys, values, k_pages, v_pages, tables = _differential_case(torch.bfloat16, heads, kv_heads, dim, vdim, lengths,
+                                                                                 queries, page_size, 31, spike)
+            slices = [SequenceSlice(f"r{s}", [0] * count, length - count, [], [tables[s, :-(-length // page_size)].tolist()], 0)
+                      for s, (length, count) in enumerate(zip(lengths, new_tokens))]
+            batch = build_batch(slices, 1, DEVICE)
+            q_cols = heads * 2 * dim
+            packed = torch.zeros((len(queries), -(-(q_cols + 8 + heads) // 8) * 8), dtype=torch.bfloat16)
+            packed[:, :q_cols] = q.reshape(len(queries), q_cols)
+            packed[:, q_cols + 8:q_cols + 8 + heads] = gate
+            want, maps = _differential_plain(q, gate, keys, values, queries, heads, kv_heads, scale, cap, window, lam, eps, out_scale, True)
+            got = {}
+            for kernel in ("mma", "generic"):
+                before, attention_bf16.DIFF_KERNEL = attention_bf16.DIFF_KERNEL, kernel
+                try:
+                    got[kernel] = ops.attention_diff(packed.to(DEVICE), q_cols + 8, batch, batch.block_tables[0], k_pages.to(DEVICE),
+                                                     v_pages.to(DEVICE), heads, kv_heads, dim, vdim, scale, cap, window, lam, eps,
+                                                     out_scale).cpu().double()
+                finally:
+                    attention_bf16.DIFF_KERNEL = before
+            torch.cuda.synchronize()
+            check_wait_errors()
+            for kernel, out in got.items():
+                error = (out - want).abs().max(dim=-1).values / want.abs().max(dim=-1).values.clamp_min(0.05)
+                assert error.max() < 1e-2, f"{kernel}, spike {spike}: row {int(error.argmax())} of {len(queries)} differs by {float(error.max()):.2e}"
+            if spike is not None and window != 1:
+                first, p = maps[last_query][spike[2]]
+                assert (float(p[spike[1] - first]) > 0.9) if spike[1] >= first else (float(p.max()) < 0.9)
+    assert not torch.equal(got["mma"], got["generic"])      # two kernels really ran
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
