@@ -17,6 +17,13 @@
 // and leaves its partial o; (3) the warps add the partitions' parts in a fixed order, normalise, gate and store.  The
 // order of every sum depends on the sizes alone, so a token's result does not depend on how the prompt was cut or on
 // what else is in the batch.
+//
+// Long portions can also be walked segment by segment in parallel (`llm_gla_recurrent` with a segment length): pass A
+// runs every segment but the last from a zero state and leaves its end state and the product of its decays; a scan adds
+// them up, S_in(k+1) = D_k S_in(k) + S_local(k), which gives every segment the state it starts from; pass C runs the
+// segments again from those states and writes the outputs.  Twice the arithmetic, all of it still 32-bit, on as many
+// blocks as there are segments; sums are then grouped by segment, so results agree with the one-pass form to rounding,
+// not bit for bit (the 32-bit path keeps the one-pass form).
 #include "common.cuh"
 
 #define GLA_TOKENS 8
@@ -33,17 +40,35 @@ struct GlaArgs {
     void* out;              // [N, heads * vdim]
     int heads, dim, vdim, partitions, padded_dim, column_threads;
     float inverse_tau, q_scale, eps;
+    int segment, max_segments;   // segmented form: tokens per segment, segments the scratch has room for per sequence
+    float* segment_state;        // [S, max_segments, heads, dim, vdim]
+    float* segment_decay;        // [S, max_segments, heads, dim]
 };
 
-template <typename T, typename W, int R>
+// MODE 0: a sequence's tokens in one pass, from and into its state slot.  1: pass A of the segmented form.  3: pass C.
+enum : int { GLA_ONE_PASS = 0, GLA_LOCAL = 1, GLA_OUTPUT = 3 };
+
+template <typename T, typename W, int R, int MODE>
 __global__ void __launch_bounds__(R == 128 ? 256 : 512) gla_recurrent_kernel(GlaArgs a) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float4 gla_shared_raw[];
     float* shared = reinterpret_cast<float*>(gla_shared_raw);
     const int seq = blockIdx.x, head = blockIdx.y;
-    const int begin = a.q_start[seq], end = a.q_start[seq + 1];
+    int begin = a.q_start[seq], end = a.q_start[seq + 1];
     if (begin >= end) return;
+    bool last_segment = true;
+    size_t segment_index = 0;
+    if (MODE != GLA_ONE_PASS) {
+        const int segments = (end - begin + a.segment - 1) / a.segment;
+        const int segment = blockIdx.z;
+        if (segment >= segments) return;
+        last_segment = segment == segments - 1;
+        if (MODE == GLA_LOCAL && last_segment) return;      // nobody needs the state a zero start leaves behind the last one
+        begin += segment * a.segment;
+        end = min(end, begin + a.segment);
+        segment_index = ((size_t)seq * a.max_segments + segment) * a.heads + head;
+    }
     const int dim = a.dim, vdim = a.vdim, padded = a.padded_dim;
     float* q_s = shared;                                   // [GLA_TOKENS][padded]
     float* k_s = q_s + GLA_TOKENS * padded;
@@ -57,9 +82,15 @@ __global__ void __launch_bounds__(R == 128 ? 256 : 512) gla_recurrent_kernel(Gla
     const float* z = a.z;
 
     float S[R];
+    float decay[MODE == GLA_LOCAL ? R : 1];      // pass A: the product of the segment's decays, row by row
     float* state = a.state + ((size_t)a.state_slots[seq] * a.heads + head) * dim * vdim;
+    float* segment_state = a.segment_state + segment_index * dim * vdim;
+    const float* source = MODE == GLA_OUTPUT ? segment_state : state;
 #pragma unroll
-    for (int i = 0; i < R; ++i) S[i] = (owner && row0 + i < dim) ? state[(size_t)(row0 + i) * vdim + column] : 0.0f;
+    for (int i = 0; i < R; ++i) {
+        S[i] = (MODE != GLA_LOCAL && owner && row0 + i < dim) ? source[(size_t)(row0 + i) * vdim + column] : 0.0f;
+        if (MODE == GLA_LOCAL) decay[i] = 1.0f;
+    }
 
     for (int first = begin; first < end; first += GLA_TOKENS) {
         const int count = min(GLA_TOKENS, end - first);
@@ -100,14 +131,22 @@ __global__ void __launch_bounds__(R == 128 ? 256 : 512) gla_recurrent_kernel(Gla
                     S[4 * i + 1] = fmaf(aa.y, S[4 * i + 1], kk.y * vj);
                     S[4 * i + 2] = fmaf(aa.z, S[4 * i + 2], kk.z * vj);
                     S[4 * i + 3] = fmaf(aa.w, S[4 * i + 3], kk.w * vj);
-                    o = fmaf(S[4 * i + 0], qq.x, o);
-                    o = fmaf(S[4 * i + 1], qq.y, o);
-                    o = fmaf(S[4 * i + 2], qq.z, o);
-                    o = fmaf(S[4 * i + 3], qq.w, o);
+                    if (MODE == GLA_LOCAL) {
+                        decay[4 * i + 0] *= aa.x;
+                        decay[4 * i + 1] *= aa.y;
+                        decay[4 * i + 2] *= aa.z;
+                        decay[4 * i + 3] *= aa.w;
+                    } else {
+                        o = fmaf(S[4 * i + 0], qq.x, o);
+                        o = fmaf(S[4 * i + 1], qq.y, o);
+                        o = fmaf(S[4 * i + 2], qq.z, o);
+                        o = fmaf(S[4 * i + 3], qq.w, o);
+                    }
                 }
-                part_s[((size_t)partition * GLA_TOKENS + t) * vdim + column] = o;
+                if (MODE != GLA_LOCAL) part_s[((size_t)partition * GLA_TOKENS + t) * vdim + column] = o;
             }
         }
+        if (MODE == GLA_LOCAL) continue;
         __syncthreads();
         const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
         for (int t = warp; t < count; t += warps) {
@@ -128,10 +167,50 @@ __global__ void __launch_bounds__(R == 128 ? 256 : 512) gla_recurrent_kernel(Gla
             }
         }
     }
-    if (owner) {
+    if (owner && (MODE == GLA_LOCAL || last_segment)) {
+        float* target = MODE == GLA_LOCAL ? segment_state : state;
 #pragma unroll
         for (int i = 0; i < R; ++i)
-            if (row0 + i < dim) state[(size_t)(row0 + i) * vdim + column] = S[i];
+            if (row0 + i < dim) target[(size_t)(row0 + i) * vdim + column] = S[i];
+        if (MODE == GLA_LOCAL && column == 0) {
+#pragma unroll
+            for (int i = 0; i < R; ++i)
+                if (row0 + i < dim) a.segment_decay[segment_index * dim + row0 + i] = decay[i];
+        }
+    }
+}
+
+// The scan between the passes: per (sequence, head), S_in(0) is the slot's state and S_in(k + 1) = D_k S_in(k) + S_local(k);
+// S_in(k) takes S_local(k)'s place in the scratch.
+template <int R>
+__global__ void __launch_bounds__(R == 128 ? 256 : 512) gla_scan_kernel(GlaArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    const int seq = blockIdx.x, head = blockIdx.y;
+    const int tokens = a.q_start[seq + 1] - a.q_start[seq];
+    if (tokens <= 0) return;
+    const int segments = (tokens + a.segment - 1) / a.segment;
+    const int dim = a.dim, vdim = a.vdim;
+    const int column = threadIdx.x % a.column_threads, partition = threadIdx.x / a.column_threads;
+    const int row0 = partition * R;
+    if (column >= vdim || partition >= a.partitions) return;
+    const float* state = a.state + ((size_t)a.state_slots[seq] * a.heads + head) * dim * vdim;
+    float S[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) S[i] = row0 + i < dim ? state[(size_t)(row0 + i) * vdim + column] : 0.0f;
+    for (int k = 0; k < segments; ++k) {
+        const size_t index = ((size_t)seq * a.max_segments + k) * a.heads + head;
+        float* place = a.segment_state + index * dim * vdim;
+        const float* decay = a.segment_decay + index * dim;
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            if (row0 + i < dim) {
+                float* cell = place + (size_t)(row0 + i) * vdim + column;
+                const float local = k + 1 < segments ? *cell : 0.0f;
+                *cell = S[i];
+                if (k + 1 < segments) S[i] = fmaf(decay[row0 + i], S[i], local);
+            }
+        }
     }
 }
 
@@ -154,7 +233,8 @@ LLM_EXPORT int llm_gla_supports(int dim, int vdim) {
 LLM_EXPORT int llm_gla_recurrent(const void* proj, int row_width, int q_offset, int k_offset, int v_offset, int g_offset,
                                  const float* z, const float* z_bias, const void* weight, float* state, const int* state_slots,
                                  const int* q_start, void* out, int n_seqs, int heads, int dim, int vdim, float inverse_tau,
-                                 float q_scale, float eps, int dtype, int weight_dtype, cudaStream_t stream) {
+                                 float q_scale, float eps, int dtype, int weight_dtype, int segment, int max_segments,
+                                 float* segment_state, float* segment_decay, cudaStream_t stream) {
     if (n_seqs == 0) return LLM_OK;
     if (!llm_gla_supports(dim, vdim) || heads <= 0) {
         llm_set_error("gla_recurrent: %d heads of %d key and %d value channels are not supported", heads, dim, vdim);
@@ -169,16 +249,32 @@ LLM_EXPORT int llm_gla_recurrent(const void* proj, int row_width, int q_offset, 
     a.partitions = (dim + rows - 1) / rows;
     a.padded_dim = a.partitions * rows;
     a.inverse_tau = inverse_tau; a.q_scale = q_scale; a.eps = eps;
+    a.segment = segment; a.max_segments = max_segments; a.segment_state = segment_state; a.segment_decay = segment_decay;
+    const bool segmented = segment > 0;
+    if (segmented && (max_segments <= 0 || !segment_state || !segment_decay)) {
+        llm_set_error("gla_recurrent: the segmented form needs its scratch");
+        return LLM_REFUSED;
+    }
     const int threads = a.partitions * a.column_threads;
     const size_t shared = ((size_t)3 * GLA_TOKENS * a.padded_dim + (size_t)GLA_TOKENS * vdim + (size_t)a.partitions * GLA_TOKENS * vdim) * sizeof(float);
-    dim3 grid(n_seqs, heads);
-#define GLA_LAUNCH(R)                                                                                                   \
+    dim3 grid(n_seqs, heads, segmented ? max_segments : 1);
+#define GLA_LAUNCH_MODE(R, MODE)                                                                                        \
     do {                                                                                                                \
         if (shared > 40 * 1024) {                                                                                       \
-            const int status = llm_raise_shared_limit((const void*)gla_recurrent_kernel<T, W, R>, shared, "gla_recurrent"); \
+            const int status = llm_raise_shared_limit((const void*)gla_recurrent_kernel<T, W, R, MODE>, shared, "gla_recurrent"); \
             if (status != LLM_OK) return status;                                                                        \
         }                                                                                                               \
-        llm_launch(gla_recurrent_kernel<T, W, R>, grid, threads, shared, stream, a);                                    \
+        llm_launch(gla_recurrent_kernel<T, W, R, MODE>, grid, threads, shared, stream, a);                              \
+    } while (0)
+#define GLA_LAUNCH(R)                                                                                                   \
+    do {                                                                                                                \
+        if (!segmented) {                                                                                               \
+            GLA_LAUNCH_MODE(R, GLA_ONE_PASS);                                                                           \
+        } else {                                                                                                        \
+            GLA_LAUNCH_MODE(R, GLA_LOCAL);                                                                              \
+            llm_launch(gla_scan_kernel<R>, dim3(n_seqs, heads), threads, 0, stream, a);                                 \
+            GLA_LAUNCH_MODE(R, GLA_OUTPUT);                                                                             \
+        }                                                                                                               \
     } while (0)
     LLM_DISPATCH_DTYPE_WEIGHT(dtype, weight_dtype, {
         if (rows == 16) GLA_LAUNCH(16);
@@ -187,5 +283,6 @@ LLM_EXPORT int llm_gla_recurrent(const void* proj, int row_width, int q_offset, 
         else GLA_LAUNCH(128);
     });
 #undef GLA_LAUNCH
+#undef GLA_LAUNCH_MODE
     return llm_check_launch("gla_recurrent");
 }

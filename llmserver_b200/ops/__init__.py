@@ -386,7 +386,7 @@ def gla_supported(dim: int, value_dim: int) -> bool:
 
 def gla_recurrent(proj: torch.Tensor, q_column: int, k_column: int, v_column: int, g_column: int, z: torch.Tensor,
                   z_bias: Optional[torch.Tensor], weight: torch.Tensor, state: torch.Tensor, batch, heads: int, dim: int,
-                  value_dim: int, tau: float, q_scale: float, eps: float) -> torch.Tensor:
+                  value_dim: int, tau: float, q_scale: float, eps: float, segment: Optional[int] = None) -> torch.Tensor:
     """The gated-linear-attention recurrence over a step's tokens, sequence by sequence, from and into each sequence's
     slot of ``state`` (float32 [slots, heads, dim, value_dim]):
 
@@ -394,7 +394,11 @@ def gla_recurrent(proj: torch.Tensor, q_column: int, k_column: int, v_column: in
         out   = o / sqrt(mean(o^2) + eps) * weight * silu(g)          per head, over value_dim
 
     q, k (heads * dim columns each), v and g (heads * value_dim) start at the given columns of ``proj``; ``z`` is
-    float32 [N, heads * dim] in either path.  Returns [N, heads * value_dim] in the activation type; the recurrence itself is 32-bit."""
+    float32 [N, heads * dim] in either path.  Returns [N, heads * value_dim] in the activation type; the recurrence itself is 32-bit.
+
+    ``segment``: tokens per segment of the form that walks a long portion's segments in parallel (two passes and a scan
+    between them; results equal to rounding).  None: chosen here, for bfloat16 steps whose longest portion spans several
+    segments; 0: always the one-pass form, which is also what the 32-bit path runs."""
     check(proj, "packed projection")
     tokens, row_width = proj.shape
     check(z, "decay projection", torch.float32, heads * dim)
@@ -408,11 +412,30 @@ def gla_recurrent(proj: torch.Tensor, q_column: int, k_column: int, v_column: in
         if column < 0 or column + size > row_width:
             raise KernelError(f"columns {column}..{column + size} lie outside a row of {row_width}")
     out = torch.empty((tokens, heads * value_dim), dtype=proj.dtype, device=proj.device)
+    longest = int(batch.max_q_len)
+    if segment is None:
+        # at most GLA_MAX_SEGMENTS segments per sequence, none shorter than GLA_SEGMENT tokens
+        segment = 0 if proj.dtype != torch.bfloat16 or longest < 2 * GLA_SEGMENT else max(GLA_SEGMENT, -(-longest // GLA_MAX_SEGMENTS))
+    segments, segment_state, segment_decay = 0, None, None
+    if segment:
+        segments = -(-longest // segment)
+        key = ("gla_segments", batch.n_seqs, segments, heads, dim, value_dim)
+        scratch = batch.scratch.get(key)
+        if scratch is None:
+            scratch = (torch.empty((batch.n_seqs, segments, heads, dim, value_dim), dtype=torch.float32, device=proj.device),
+                       torch.empty((batch.n_seqs, segments, heads, dim), dtype=torch.float32, device=proj.device))
+            batch.scratch[key] = scratch
+        segment_state, segment_decay = scratch
     call("llm_gla_recurrent", proj.data_ptr(), row_width, int(q_column), int(k_column), int(v_column), int(g_column),
          z.data_ptr(), pointer(z_bias), weight.data_ptr(), state.data_ptr(), batch.state_slots.data_ptr(), batch.q_start.data_ptr(),
          out.data_ptr(), batch.n_seqs, int(heads), int(dim), int(value_dim), 1.0 / float(tau), float(q_scale), float(eps),
-         dtype_code(proj.dtype), dtype_code(weight.dtype), stream_handle())
+         dtype_code(proj.dtype), dtype_code(weight.dtype), int(segment), int(segments), pointer(segment_state), pointer(segment_decay),
+         stream_handle())
     return out
+
+
+GLA_SEGMENT = 64          # fewest tokens per segment of the segmented recurrence
+GLA_MAX_SEGMENTS = 128    # most segments per sequence (the scratch holds a state per segment)
 
 
 def head_linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:

@@ -412,27 +412,31 @@ def test_gated_linear_attention_kernel(dtype, heads, dim, vdim, tau):
         return out, S
 
     slots = [2, 0, 3]
-    state = torch.zeros((4, heads, dim, vdim), dtype=torch.float32, device=DEVICE)
-    state[1] = 7.0          # nobody's slot: must stay as it is
     tolerance = 2e-5 if dtype == torch.float32 else 2e-2
-    # the step before: sequences 1 and 2 run their earlier tokens (sequence 2 first, to change the slot order)
-    earlier = [(2, lengths[2][0]), (1, lengths[1][0])]
-    batch = build_batch([SequenceSlice(f"r{s}", [0] * count, 0, [], [[0]], slots[s]) for s, count in earlier], 1, DEVICE)
-    rows = torch.cat([proj[s][:count] for s, count in earlier]).to(DEVICE)
-    ops.gla_recurrent(rows, *columns, torch.cat([z[s][:count] for s, count in earlier]).to(DEVICE), z_bias.to(DEVICE), weight.to(DEVICE),
-                      state, batch, heads, dim, vdim, tau, q_scale, eps)
-    # this step
-    batch = build_batch([SequenceSlice(f"r{s}", [0] * now, before, [], [[0]], slots[s]) for s, (before, now) in enumerate(lengths)], 1, DEVICE)
-    rows = torch.cat([proj[s][before:] for s, (before, _) in enumerate(lengths)]).to(DEVICE)
-    got = ops.gla_recurrent(rows, *columns, torch.cat([z[s][before:] for s, (before, _) in enumerate(lengths)]).to(DEVICE),
-                            z_bias.to(DEVICE), weight.to(DEVICE), state, batch, heads, dim, vdim, tau, q_scale, eps).cpu().double()
-    at = 0
-    for s, (before, now) in enumerate(lengths):
-        want, last = plain_run(s, before + now)
-        assert torch.allclose(got[at:at + now], want[before:], atol=tolerance, rtol=tolerance), f"sequence {s}"
-        assert torch.allclose(state[slots[s]].cpu().double(), last, atol=2e-4, rtol=2e-4), f"state of sequence {s}"
-        at += now
-    assert bool((state[1] == 7.0).all())
+    # segment 0: one pass over a sequence's tokens; 8 and 16: the form that walks segments in parallel (here 5, 2 and 1
+    # segments, or 3, 1 and 1), which must agree to rounding
+    for segment in (0, 8, 16):
+        state = torch.zeros((4, heads, dim, vdim), dtype=torch.float32, device=DEVICE)
+        state[1] = 7.0          # nobody's slot: must stay as it is
+        # the step before: sequences 1 and 2 run their earlier tokens (sequence 2 first, to change the slot order)
+        earlier = [(2, lengths[2][0]), (1, lengths[1][0])]
+        batch = build_batch([SequenceSlice(f"r{s}", [0] * count, 0, [], [[0]], slots[s]) for s, count in earlier], 1, DEVICE)
+        rows = torch.cat([proj[s][:count] for s, count in earlier]).to(DEVICE)
+        ops.gla_recurrent(rows, *columns, torch.cat([z[s][:count] for s, count in earlier]).to(DEVICE), z_bias.to(DEVICE),
+                          weight.to(DEVICE), state, batch, heads, dim, vdim, tau, q_scale, eps, segment=segment)
+        # this step
+        batch = build_batch([SequenceSlice(f"r{s}", [0] * now, before, [], [[0]], slots[s]) for s, (before, now) in enumerate(lengths)], 1, DEVICE)
+        rows = torch.cat([proj[s][before:] for s, (before, _) in enumerate(lengths)]).to(DEVICE)
+        got = ops.gla_recurrent(rows, *columns, torch.cat([z[s][before:] for s, (before, _) in enumerate(lengths)]).to(DEVICE),
+                                z_bias.to(DEVICE), weight.to(DEVICE), state, batch, heads, dim, vdim, tau, q_scale, eps,
+                                segment=segment).cpu().double()
+        at = 0
+        for s, (before, now) in enumerate(lengths):
+            want, last = plain_run(s, before + now)
+            assert torch.allclose(got[at:at + now], want[before:], atol=tolerance, rtol=tolerance), f"sequence {s}, segment {segment}"
+            assert torch.allclose(state[slots[s]].cpu().double(), last, atol=2e-4, rtol=2e-4), f"state of sequence {s}, segment {segment}"
+            at += now
+        assert bool((state[1] == 7.0).all())
 
 
 # ------------------------------------------------------------------------------------------------ whole models
