@@ -3,15 +3,17 @@
 //     s_m = cap(q_m . k_m * scale),  a_m = softmax(s_m) V  (m = 1, 2),  o = a_1 - lambda * a_2,
 //     out = o / sqrt(mean(o^2) + eps) * out_scale * sigmoid(gate)
 //
-// Rows of a tile are (token, head of the group) pairs of one sequence and one key/value head, so a key tile is read
-// once for all query heads that share it; a decode step's tile is the group's heads of one token.  A block has 8
-// warps = row tiles x key splits (4 x 2 where a sequence brings a portion, 1 x 8 for single tokens).  Every warp runs
-// a pipeline of its own: cp.async brings a tile of keys (both maps) and values into the warp's shared memory, the warp
-// forms S for map 1, updates its running maximum and sum, multiplies P V, and does the same for map 2 on the same V
-// tile; there is no block barrier inside the key loop.  Attention weights stay 32-bit-grade through the P V product:
-// each is carried as the sum of two bfloat16 numbers (its rounding and the rounding of the rest), two MMAs.  At the end
-// the splits' partial results meet in shared memory; one warp per row merges them, subtracts the maps, normalises the
-// head, applies the gate and stores.
+// Rows of a tile are (token, head of the group) pairs of one sequence and one key/value head, so a decode step's tile
+// is the group's heads of one token.  A warp owns 16 rows and ONE map: for a tile of 16 keys it forms S = Q_m K_m^T,
+// updates its running maximum and sum and multiplies P V; the warp beside it does the same for the other map.  A block
+// has 8 warps = row tiles x 2 maps x key splits: 2 x 2 x 2 for steps with prompt portions (measured ahead of 4 x 2 x 1
+// and 1 x 2 x 4 at 2048 tokens with a window of 1024), 1 x 2 x 4 for steps of single tokens.  Every warp runs a pipeline of its own, cp.async into shared memory of its own, with no block barrier
+// inside the key loop; with 128 registers a thread two blocks share an SM, which is what hides the latencies of
+// ldmatrix, MMA and the exponentials (one warp with both maps needed 255 registers, one block per SM, and ran the
+// tensor pipe at 23 %).  Attention weights stay 32-bit-grade through the P V product: each is carried as the sum of two
+// bfloat16 numbers (its rounding and the rounding of the rest), two MMAs.  At the end the warps' partial results meet
+// in shared memory; one warp per row merges the splits, subtracts the maps, normalises the head, applies the gate and
+// stores.
 //
 // Sizes: units of 64 or 128 elements per map, values of 64 or 128; any group, window, page size (pages need not
 // align with tiles: every key's page is looked up).  Other sizes run attention_diff.cu.
@@ -69,23 +71,40 @@ struct DiffParams {
 };
 
 constexpr int kWarps = 8;
+constexpr int kKeys = 16;    // keys per tile
 constexpr int kPad = 8;      // elements of padding per shared-memory row: rows 16 bytes apart modulo 128, conflict-free ldmatrix
 
 template <int DIM, int DV>
 struct DiffShape {
-    static constexpr int kKeys = DIM == 64 ? 32 : 16;                 // keys per tile
-    static constexpr int kKeyRow = 2 * DIM + kPad, kValueRow = DV + kPad;
+    static constexpr int kKeyRow = DIM + kPad, kValueRow = DV + kPad;      // a warp holds its own map's half of a key row
     static constexpr int kQBytes = 16 * kKeyRow * 2, kKBytes = kKeys * kKeyRow * 2, kVBytes = kKeys * kValueRow * 2;
-    static constexpr int kWarpBytes = kQBytes + kKBytes + kVBytes;    // also holds a warp's partial result at the end
-    static_assert(kWarpBytes >= 2 * 16 * DV * 4 + 2 * 16 * 2 * 4, "a warp's partial result must fit its shared memory");
+    static constexpr int kPartialBytes = 16 * DV * 4 + 16 * 2 * 4;         // a warp's O [16 rows][DV], then max and sum [16][2]
+    static constexpr int kTileBytes = kQBytes + kKBytes + kVBytes;
+    static constexpr int kWarpBytes = kTileBytes > kPartialBytes ? kTileBytes : kPartialBytes;
 };
 
+// 1 - 2 / (exp(2x) + 1): the hardware exponential and a fast division; absolute error of a few 1e-7, exact limits
+__device__ __forceinline__ float fast_tanh(float x) { return 1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f); }
+
+// Where key `key` of the sequence lies in the pages (in slots of one key/value head); keys behind the context read the
+// last key, and are masked by their scores.
+__device__ __forceinline__ long long slot_of_key(const DiffParams& p, const int* table, int key, int context, int kv_head) {
+    key = min(key, context - 1);
+    int page = table[key / p.page_size];
+    if ((unsigned)page >= (unsigned)p.num_pages) {
+        atomicExch(p.error_flag, 5);
+        page = 0;
+    }
+    return ((long long)page * p.n_kv_heads + kv_head) * p.page_size + key % p.page_size;
+}
+
 template <int DIM, int DV>
-__global__ void __launch_bounds__(kWarps * 32) attention_diff_mma_kernel(DiffParams p) {
+__global__ void __launch_bounds__(kWarps * 32, 2) attention_diff_mma_kernel(DiffParams p) {
     pdl_trigger();
     pdl_wait();
     using Shape = DiffShape<DIM, DV>;
-    constexpr int KT = Shape::kKeys;
+    constexpr int KT = kKeys;
+    constexpr int kKeyChunks = DIM / 8, kValueChunks = DV / 8;
     extern __shared__ uint4 diff_shared_raw[];
     unsigned char* shared = reinterpret_cast<unsigned char*>(diff_shared_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -95,17 +114,19 @@ __global__ void __launch_bounds__(kWarps * 32) attention_diff_mma_kernel(DiffPar
     const int context = p.context_len[sequence];
     const int start = context - q_len;                  // position of the portion's first token
     const int total_rows = q_len * group;
-    const int row_tiles = p.row_tiles, splits = kWarps / row_tiles;
+    const int row_tiles = p.row_tiles, splits = kWarps / (2 * row_tiles);
     const int block_row0 = blockIdx.x * 16 * row_tiles;
     if (block_row0 >= total_rows) return;
-    const int tile = warp % row_tiles, split = warp / row_tiles;
+    // warp = tile + row_tiles * (map + 2 * split)
+    const int tile = warp % row_tiles, map = (warp / row_tiles) & 1, split = warp / (2 * row_tiles);
     const int row0 = block_row0 + tile * 16;
-    unsigned char* mine = shared + (size_t)warp * Shape::kWarpBytes;
+    unsigned char* mine = shared + (size_t)warp * Shape::kWarpBytes;      // the warp's tiles, and its partial result at the end
     __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(mine);
     __nv_bfloat16* k_tile = reinterpret_cast<__nv_bfloat16*>(mine + Shape::kQBytes);
     __nv_bfloat16* v_tile = reinterpret_cast<__nv_bfloat16*>(mine + Shape::kQBytes + Shape::kKBytes);
     const int* table = p.block_tables + (size_t)sequence * p.max_blocks;
     const bool tile_live = row0 < total_rows;
+    const float inverse_cap = p.cap > 0.0f ? 1.0f / p.cap : 0.0f;
 
     // this lane's two rows of the tile: the C-fragment rows lane / 4 and lane / 4 + 8
     int row_position[2];
@@ -114,57 +135,41 @@ __global__ void __launch_bounds__(kWarps * 32) attention_diff_mma_kernel(DiffPar
         const int r = row0 + (lane >> 2) + 8 * h;
         row_position[h] = r < total_rows ? start + r / group : -1;      // -1: no such row, nothing is visible
     }
-    float acc[2][DV / 8][4];
-    float running_max[2][2], running_sum[2][2];
+    float acc[DV / 8][4];
+    float running_max[2] = {-INFINITY, -INFINITY}, running_sum[2] = {0.0f, 0.0f};
 #pragma unroll
-    for (int m = 0; m < 2; ++m) {
-#pragma unroll
-        for (int j = 0; j < DV / 8; ++j) acc[m][j][0] = acc[m][j][1] = acc[m][j][2] = acc[m][j][3] = 0.0f;
-        running_max[m][0] = running_max[m][1] = -INFINITY;
-        running_sum[m][0] = running_sum[m][1] = 0.0f;
-    }
+    for (int j = 0; j < DV / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
 
     if (tile_live) {
-        // queries of the tile's 16 rows, both maps, into the warp's shared memory (rows that do not exist: zeros)
-        constexpr int kChunks = 2 * DIM / 8;
-        for (int c = lane; c < 16 * kChunks; c += 32) {
-            const int r = c / kChunks, chunk = c % kChunks, row = row0 + r;
+        // the map's queries of the tile's 16 rows into the warp's shared memory (rows that do not exist: zeros)
+        for (int c = lane; c < 16 * kKeyChunks; c += 32) {
+            const int r = c / kKeyChunks, chunk = c % kKeyChunks, row = row0 + r;
             uint4 value = make_uint4(0, 0, 0, 0);
             if (row < total_rows) {
                 const int token = begin + row / group, head = kv_head * group + row % group;
-                value = *reinterpret_cast<const uint4*>(p.q + (size_t)token * p.q_stride + (size_t)head * 2 * DIM + chunk * 8);
+                value = *reinterpret_cast<const uint4*>(p.q + (size_t)token * p.q_stride + ((size_t)head * 2 + map) * DIM + chunk * 8);
             }
             *reinterpret_cast<uint4*>(q_tile + r * Shape::kKeyRow + chunk * 8) = value;
         }
+        // the keys this warp's rows see between them, and the keys every one of its rows sees
         const int last_row = min(row0 + 15, total_rows - 1);
-        const int key_high = start + last_row / group;                                     // the last key any row sees
-        const int first_position = start + row0 / group;
-        const int key_low = p.window > 0 ? max(0, first_position - p.window + 1) : 0;       // the first key any row sees
+        const int warp_first = start + row0 / group, warp_last = start + last_row / group;     // positions of its first and last row
+        const int key_low = p.window > 0 ? max(0, warp_first - p.window + 1) : 0;
+        const int key_high = warp_last;
+        const int whole_low = p.window > 0 ? max(0, warp_last - p.window + 1) : 0, whole_high = warp_first;
         const int n_tiles = (key_high - key_low + KT) / KT;
         const int per_split = (n_tiles + splits - 1) / splits;
         const int tile_begin = split * per_split, tile_end = min(n_tiles, tile_begin + per_split);
-        const float inverse_cap = p.cap > 0.0f ? 1.0f / p.cap : 0.0f;
 
         for (int t = tile_begin; t < tile_end; ++t) {
             const int key0 = key_low + t * KT;
             __syncwarp();      // everyone has read the tile before
-            // the slot of each key of the tile (lane = key); keys behind the context read the last key and are masked
-            long long slot = 0;
-            if (lane < KT) {
-                const int key = min(key0 + lane, context - 1);
-                int page = table[key / p.page_size];
-                if ((unsigned)page >= (unsigned)p.num_pages) {
-                    atomicExch(p.error_flag, 5);
-                    page = 0;
-                }
-                slot = ((long long)page * p.n_kv_heads + kv_head) * p.page_size + key % p.page_size;
-            }
-            constexpr int kKeyChunks = 2 * DIM / 8, kValueChunks = DV / 8;
+            const long long slot = lane < KT ? slot_of_key(p, table, key0 + lane, context, kv_head) : 0;      // lane = key
 #pragma unroll
             for (int c = lane; c < KT * kKeyChunks; c += 32) {
                 const int key = c / kKeyChunks, chunk = c % kKeyChunks;
                 const long long at = __shfl_sync(0xffffffffu, slot, key);
-                copy_async_16(shared_address(k_tile + key * Shape::kKeyRow + chunk * 8), p.k_pages + at * (2 * DIM) + chunk * 8);
+                copy_async_16(shared_address(k_tile + key * Shape::kKeyRow + chunk * 8), p.k_pages + (at * 2 + map) * DIM + chunk * 8);
             }
 #pragma unroll
             for (int c = lane; c < KT * kValueChunks; c += 32) {
@@ -174,129 +179,127 @@ __global__ void __launch_bounds__(kWarps * 32) attention_diff_mma_kernel(DiffPar
             }
             copy_async_wait_all();
             __syncwarp();
+            // every key of the tile is visible to every row of the warp: no score needs masking
+            const bool whole = key0 >= whole_low && key0 + KT - 1 <= whole_high && row0 + 15 < total_rows;
 
+            // S = Q_m K_m^T for 16 rows x KT keys
+            float s[KT / 8][4];
 #pragma unroll
-            for (int m = 0; m < 2; ++m) {
-                // S = Q_m K_m^T for 16 rows x KT keys
-                float s[KT / 8][4];
+            for (int j = 0; j < KT / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
 #pragma unroll
-                for (int j = 0; j < KT / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+            for (int ks = 0; ks < DIM / 16; ++ks) {
+                uint32_t a[4], b[4];
+                load_matrices(a, shared_address(q_tile + ((lane & 7) + 8 * ((lane >> 3) & 1)) * Shape::kKeyRow + ks * 16 + 8 * (lane >> 4)));
+                load_matrices(b, shared_address(k_tile + ((lane & 7) + 8 * (lane >> 4)) * Shape::kKeyRow + ks * 16 + 8 * ((lane >> 3) & 1)));
+                multiply_add(s[0], a, b[0], b[1]);
+                multiply_add(s[1], a, b[2], b[3]);
+            }
+            // scale, cap, mask; the rows' maxima
+            float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-                for (int ks = 0; ks < DIM / 16; ++ks) {
-                    uint32_t a[4];
-                    load_matrices(a, shared_address(q_tile + ((lane & 7) + 8 * ((lane >> 3) & 1)) * Shape::kKeyRow + m * DIM + ks * 16 +
-                                                    8 * (lane >> 4)));
+            for (int j = 0; j < KT / 8; ++j) {
 #pragma unroll
-                    for (int jp = 0; jp < KT / 16; ++jp) {
-                        uint32_t b[4];
-                        load_matrices(b, shared_address(k_tile + (jp * 16 + (lane & 7) + 8 * (lane >> 4)) * Shape::kKeyRow + m * DIM +
-                                                        ks * 16 + 8 * ((lane >> 3) & 1)));
-                        multiply_add(s[2 * jp], a, b[0], b[1]);
-                        multiply_add(s[2 * jp + 1], a, b[2], b[3]);
-                    }
-                }
-                // scale, cap, mask; the rows' maxima
-                float tile_max[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-                for (int j = 0; j < KT / 8; ++j) {
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int h = e >> 1;
+                for (int e = 0; e < 4; ++e) {
+                    const int h = e >> 1;
+                    float value = s[j][e] * p.scale;
+                    if (p.cap > 0.0f) value = p.cap * fast_tanh(value * inverse_cap);
+                    if (!whole) {
                         const int key = key0 + 8 * j + 2 * (lane & 3) + (e & 1);
-                        float value = s[j][e] * p.scale;
-                        if (p.cap > 0.0f) value = p.cap * tanhf(value * inverse_cap);
                         const bool seen = key <= row_position[h] && (p.window <= 0 || key > row_position[h] - p.window);
                         value = seen ? value : -INFINITY;
-                        s[j][e] = value;
-                        tile_max[h] = fmaxf(tile_max[h], value);
                     }
+                    s[j][e] = value;
+                    tile_max[h] = fmaxf(tile_max[h], value);
                 }
-                float correction[2];
+            }
+            float correction[2];
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 1));
-                    tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 2));
-                    const float new_max = fmaxf(running_max[m][h], tile_max[h]);
-                    // a row that has seen nothing yet keeps a maximum of -inf: subtract 0 there, its weights are exp(-inf) = 0
-                    const float safe_max = new_max == -INFINITY ? 0.0f : new_max;
-                    correction[h] = __expf(running_max[m][h] - safe_max);      // exp(-inf) = 0 on the first tile
-                    running_max[m][h] = new_max;
-                    tile_max[h] = safe_max;
+            for (int h = 0; h < 2; ++h) {
+                tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 1));
+                tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 2));
+                const float new_max = fmaxf(running_max[h], tile_max[h]);
+                // a row that has seen nothing yet keeps a maximum of -inf: subtract 0 there, its weights are exp(-inf) = 0
+                const float safe_max = new_max == -INFINITY ? 0.0f : new_max;
+                correction[h] = __expf(running_max[h] - safe_max);      // exp(-inf) = 0 on the first tile
+                running_max[h] = new_max;
+                tile_max[h] = safe_max;
+            }
+            float tile_sum[2] = {0.0f, 0.0f};
+#pragma unroll
+            for (int j = 0; j < KT / 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float weight = __expf(s[j][e] - tile_max[e >> 1]);
+                    s[j][e] = weight;
+                    tile_sum[e >> 1] += weight;
                 }
-                float tile_sum[2] = {0.0f, 0.0f};
+            }
 #pragma unroll
-                for (int j = 0; j < KT / 8; ++j) {
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float weight = __expf(s[j][e] - tile_max[e >> 1]);
-                        s[j][e] = weight;
-                        tile_sum[e >> 1] += weight;
-                    }
-                }
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    tile_sum[h] += __shfl_xor_sync(0xffffffffu, tile_sum[h], 1);
-                    tile_sum[h] += __shfl_xor_sync(0xffffffffu, tile_sum[h], 2);
-                    running_sum[m][h] = running_sum[m][h] * correction[h] + tile_sum[h];
-                }
+            for (int h = 0; h < 2; ++h) {
+                tile_sum[h] += __shfl_xor_sync(0xffffffffu, tile_sum[h], 1);
+                tile_sum[h] += __shfl_xor_sync(0xffffffffu, tile_sum[h], 2);
+                running_sum[h] = running_sum[h] * correction[h] + tile_sum[h];
+            }
+            if (correction[0] != 1.0f || correction[1] != 1.0f) {     // a maximum moved
 #pragma unroll
                 for (int j = 0; j < DV / 8; ++j) {
-                    acc[m][j][0] *= correction[0];
-                    acc[m][j][1] *= correction[0];
-                    acc[m][j][2] *= correction[1];
-                    acc[m][j][3] *= correction[1];
+                    acc[j][0] *= correction[0];
+                    acc[j][1] *= correction[0];
+                    acc[j][2] *= correction[1];
+                    acc[j][3] *= correction[1];
                 }
-                // O_m += P V with P as two bfloat16 parts
+            }
+            // O += P V with P as two bfloat16 parts (KT = 16 keys: one k-step)
+            uint32_t high[4], low[4];
+            high[0] = pack_pair(s[0][0], s[0][1]);
+            high[1] = pack_pair(s[0][2], s[0][3]);
+            high[2] = pack_pair(s[1][0], s[1][1]);
+            high[3] = pack_pair(s[1][2], s[1][3]);
+            low[0] = pack_rest(s[0][0], s[0][1], high[0]);
+            low[1] = pack_rest(s[0][2], s[0][3], high[1]);
+            low[2] = pack_rest(s[1][0], s[1][1], high[2]);
+            low[3] = pack_rest(s[1][2], s[1][3], high[3]);
+            // two column pairs at a time, the four MMAs of one part before those of the other: an accumulator's next
+            // MMA comes four instructions after its last
 #pragma unroll
-                for (int kk = 0; kk < KT / 16; ++kk) {
-                    uint32_t high[4], low[4];
-                    high[0] = pack_pair(s[2 * kk][0], s[2 * kk][1]);
-                    high[1] = pack_pair(s[2 * kk][2], s[2 * kk][3]);
-                    high[2] = pack_pair(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-                    high[3] = pack_pair(s[2 * kk + 1][2], s[2 * kk + 1][3]);
-                    low[0] = pack_rest(s[2 * kk][0], s[2 * kk][1], high[0]);
-                    low[1] = pack_rest(s[2 * kk][2], s[2 * kk][3], high[1]);
-                    low[2] = pack_rest(s[2 * kk + 1][0], s[2 * kk + 1][1], high[2]);
-                    low[3] = pack_rest(s[2 * kk + 1][2], s[2 * kk + 1][3], high[3]);
-#pragma unroll
-                    for (int jp = 0; jp < DV / 16; ++jp) {
-                        uint32_t b[4];
-                        load_matrices_transposed(b, shared_address(v_tile + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * Shape::kValueRow +
-                                                                   jp * 16 + 8 * (lane >> 4)));
-                        multiply_add(acc[m][2 * jp], high, b[0], b[1]);
-                        multiply_add(acc[m][2 * jp], low, b[0], b[1]);
-                        multiply_add(acc[m][2 * jp + 1], high, b[2], b[3]);
-                        multiply_add(acc[m][2 * jp + 1], low, b[2], b[3]);
-                    }
-                }
+            for (int jp = 0; jp < DV / 16; jp += 2) {
+                uint32_t b[4], c[4];
+                const int key_row = (lane & 7) + 8 * ((lane >> 3) & 1);
+                load_matrices_transposed(b, shared_address(v_tile + key_row * Shape::kValueRow + jp * 16 + 8 * (lane >> 4)));
+                load_matrices_transposed(c, shared_address(v_tile + key_row * Shape::kValueRow + (jp + 1) * 16 + 8 * (lane >> 4)));
+                multiply_add(acc[2 * jp], high, b[0], b[1]);
+                multiply_add(acc[2 * jp + 1], high, b[2], b[3]);
+                multiply_add(acc[2 * jp + 2], high, c[0], c[1]);
+                multiply_add(acc[2 * jp + 3], high, c[2], c[3]);
+                multiply_add(acc[2 * jp], low, b[0], b[1]);
+                multiply_add(acc[2 * jp + 1], low, b[2], b[3]);
+                multiply_add(acc[2 * jp + 2], low, c[0], c[1]);
+                multiply_add(acc[2 * jp + 3], low, c[2], c[3]);
             }
         }
         __syncwarp();
-        // the warp's partial result takes the place of its tiles: O [2 maps][16 rows][DV], then max and sum [2][16][2]
+        // the warp's partial result takes the place of its tiles: O [16 rows][DV], then max and sum [16][2]
         float* partial = reinterpret_cast<float*>(mine);
-        float* statistics = partial + 2 * 16 * DV;
+        float* statistics = partial + 16 * DV;
 #pragma unroll
-        for (int m = 0; m < 2; ++m) {
+        for (int j = 0; j < DV / 8; ++j) {
 #pragma unroll
-            for (int j = 0; j < DV / 8; ++j) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int r = (lane >> 2) + 8 * (e >> 1), column = 8 * j + 2 * (lane & 3) + (e & 1);
-                    partial[(m * 16 + r) * DV + column] = acc[m][j][e];
-                }
+            for (int e = 0; e < 4; ++e) {
+                const int r = (lane >> 2) + 8 * (e >> 1), column = 8 * j + 2 * (lane & 3) + (e & 1);
+                partial[r * DV + column] = acc[j][e];
             }
-            if ((lane & 3) == 0) {
+        }
+        if ((lane & 3) == 0) {
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int r = (lane >> 2) + 8 * h;
-                    statistics[(m * 16 + r) * 2] = running_max[m][h];
-                    statistics[(m * 16 + r) * 2 + 1] = running_sum[m][h];
-                }
+            for (int h = 0; h < 2; ++h) {
+                const int r = (lane >> 2) + 8 * h;
+                statistics[r * 2] = running_max[h];
+                statistics[r * 2 + 1] = running_sum[h];
             }
         }
     }
     __syncthreads();
-    // one warp per row: merge the splits, subtract the maps, normalise the head, gate, store
+    // one warp per row: merge the splits of each map, subtract the maps, normalise the head, gate, store
     const int block_rows = min(16 * row_tiles, total_rows - block_row0);
     for (int r = warp; r < block_rows; r += kWarps) {
         const int in_tile = r % 16, which_tile = r / 16;
@@ -305,21 +308,21 @@ __global__ void __launch_bounds__(kWarps * 32) attention_diff_mma_kernel(DiffPar
         for (int m = 0; m < 2; ++m) {
             float top = -INFINITY;
             for (int s = 0; s < splits; ++s) {
-                const float* statistics = reinterpret_cast<const float*>(shared + (size_t)(s * row_tiles + which_tile) * Shape::kWarpBytes) + 2 * 16 * DV;
-                top = fmaxf(top, statistics[(m * 16 + in_tile) * 2]);
+                const float* statistics = reinterpret_cast<const float*>(shared + (size_t)(which_tile + row_tiles * (m + 2 * s)) * Shape::kWarpBytes) + 16 * DV;
+                top = fmaxf(top, statistics[in_tile * 2]);
             }
             float denominator = 0.0f;
 #pragma unroll
             for (int i = 0; i < DV / 32; ++i) merged[m][i] = 0.0f;
             for (int s = 0; s < splits; ++s) {
-                const float* partial = reinterpret_cast<const float*>(shared + (size_t)(s * row_tiles + which_tile) * Shape::kWarpBytes);
-                const float* statistics = partial + 2 * 16 * DV;
-                const float own_max = statistics[(m * 16 + in_tile) * 2];
+                const float* partial = reinterpret_cast<const float*>(shared + (size_t)(which_tile + row_tiles * (m + 2 * s)) * Shape::kWarpBytes);
+                const float* statistics = partial + 16 * DV;
+                const float own_max = statistics[in_tile * 2];
                 if (own_max == -INFINITY) continue;          // this split saw no key of the row
                 const float factor = __expf(own_max - top);
-                denominator += factor * statistics[(m * 16 + in_tile) * 2 + 1];
+                denominator += factor * statistics[in_tile * 2 + 1];
 #pragma unroll
-                for (int i = 0; i < DV / 32; ++i) merged[m][i] += factor * partial[(m * 16 + in_tile) * DV + lane + 32 * i];
+                for (int i = 0; i < DV / 32; ++i) merged[m][i] += factor * partial[in_tile * DV + lane + 32 * i];
             }
             const float inverse = 1.0f / denominator;
 #pragma unroll
@@ -367,7 +370,7 @@ LLM_EXPORT int llm_attention_diff_mma(const void* q, int q_stride, const void* g
                                       const void* v_pages, const int* block_tables, int max_blocks, const int* q_start,
                                       const int* context_len, void* out, int n_seqs, int max_q_len, int n_q_heads, int n_kv_heads,
                                       int dim, int value_dim, int page_size, int num_pages, float scale, float cap, int window,
-                                      float lambda, float eps, float out_scale, int* error_flag, cudaStream_t stream) {
+                                      float lambda, float eps, float out_scale, int* error_flag, int row_tiles, cudaStream_t stream) {
     if (n_seqs == 0 || max_q_len == 0) return LLM_OK;
     if (!llm_attention_diff_mma_supports(dim, value_dim, n_q_heads, n_kv_heads) || page_size <= 0 || num_pages <= 0) {
         llm_set_error("attention_diff_mma: units of %d, values of %d, %d / %d heads are not supported", dim, value_dim, n_q_heads, n_kv_heads);
@@ -383,7 +386,9 @@ LLM_EXPORT int llm_attention_diff_mma(const void* q, int q_stride, const void* g
     p.max_blocks = max_blocks; p.q_start = q_start; p.context_len = context_len; p.out = (__nv_bfloat16*)out;
     p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.num_pages = num_pages;
     p.scale = scale; p.cap = cap; p.lambda = lambda; p.eps = eps; p.out_scale = out_scale; p.window = window;
-    p.row_tiles = max_q_len > 1 ? 4 : 1;
+    // 8: the warps share their key tiles (prompt portions); 1, 2, 4: the rest of the warps split a tile's keys
+    // 2 row tiles (and 2 key splits) for steps with prompt portions, 1 (and 4 key splits) for steps of single tokens
+    p.row_tiles = (row_tiles == 1 || row_tiles == 2 || row_tiles == 4) ? row_tiles : (max_q_len > 1 ? 2 : 1);
     p.error_flag = error_flag;
     if (dim == 64 && value_dim == 64) return launch_diff<64, 64>(p, n_seqs, max_q_len, stream);
     if (dim == 64 && value_dim == 128) return launch_diff<64, 128>(p, n_seqs, max_q_len, stream);

@@ -12,8 +12,8 @@
 // size and single decoded tokens continue it.  A slot that a new request takes over is zeroed by the cache manager.
 //
 // One block per (sequence, head).  A thread owns `R` rows of one column of S in registers; `P` such row partitions
-// cover dim.  Tokens are taken eight at a time: (1) the block stages their q, k, alpha and v in shared memory, the decay
-// and everything else that enters the recurrence in 32-bit; (2) every thread walks the eight tokens on its registers
+// cover dim.  Tokens are taken sixteen at a time: (1) the block stages their q, k, alpha and v in shared memory, the decay
+// and everything else that enters the recurrence in 32-bit; (2) every thread walks the sixteen tokens on its registers
 // and leaves its partial o; (3) the warps add the partitions' parts in a fixed order, normalise, gate and store.  The
 // order of every sum depends on the sizes alone, so a token's result does not depend on how the prompt was cut or on
 // what else is in the batch.
@@ -26,7 +26,7 @@
 // not bit for bit (the 32-bit path keeps the one-pass form).
 #include "common.cuh"
 
-#define GLA_TOKENS 8
+#define GLA_TOKENS 16
 
 struct GlaArgs {
     const void* proj;       // [N, row_width]
@@ -49,7 +49,7 @@ struct GlaArgs {
 enum : int { GLA_ONE_PASS = 0, GLA_LOCAL = 1, GLA_OUTPUT = 3 };
 
 template <typename T, typename W, int R, int MODE>
-__global__ void __launch_bounds__(R == 128 ? 256 : 512) gla_recurrent_kernel(GlaArgs a) {
+__global__ void __launch_bounds__(R == 128 ? 256 : 512, R <= 16 ? 2 : 1) gla_recurrent_kernel(GlaArgs a) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float4 gla_shared_raw[];
@@ -181,34 +181,39 @@ __global__ void __launch_bounds__(R == 128 ? 256 : 512) gla_recurrent_kernel(Gla
 }
 
 // The scan between the passes: per (sequence, head), S_in(0) is the slot's state and S_in(k + 1) = D_k S_in(k) + S_local(k);
-// S_in(k) takes S_local(k)'s place in the scratch.
-template <int R>
-__global__ void __launch_bounds__(R == 128 ? 256 : 512) gla_scan_kernel(GlaArgs a) {
+// S_in(k) takes S_local(k)'s place in the scratch.  One thread per cell of S: the cells are independent, and the
+// segments' values are loaded a few ahead of the chain of multiply-adds that needs them.
+__global__ void gla_scan_kernel(GlaArgs a) {
     pdl_trigger();
     pdl_wait();
     const int seq = blockIdx.x, head = blockIdx.y;
     const int tokens = a.q_start[seq + 1] - a.q_start[seq];
     if (tokens <= 0) return;
     const int segments = (tokens + a.segment - 1) / a.segment;
-    const int dim = a.dim, vdim = a.vdim;
-    const int column = threadIdx.x % a.column_threads, partition = threadIdx.x / a.column_threads;
-    const int row0 = partition * R;
-    if (column >= vdim || partition >= a.partitions) return;
-    const float* state = a.state + ((size_t)a.state_slots[seq] * a.heads + head) * dim * vdim;
-    float S[R];
+    const int cells = a.dim * a.vdim;
+    const int cell = blockIdx.z * blockDim.x + threadIdx.x;
+    if (cell >= cells) return;
+    const int row = cell / a.vdim;
+    float S = a.state[((size_t)a.state_slots[seq] * a.heads + head) * cells + cell];
+    const size_t first = ((size_t)seq * a.max_segments) * a.heads + head;
+    const size_t stride = a.heads;      // from one segment's index to the next's
+    constexpr int AHEAD = 4;
+    for (int k0 = 0; k0 < segments; k0 += AHEAD) {
+        float local[AHEAD], decay[AHEAD];
 #pragma unroll
-    for (int i = 0; i < R; ++i) S[i] = row0 + i < dim ? state[(size_t)(row0 + i) * vdim + column] : 0.0f;
-    for (int k = 0; k < segments; ++k) {
-        const size_t index = ((size_t)seq * a.max_segments + k) * a.heads + head;
-        float* place = a.segment_state + index * dim * vdim;
-        const float* decay = a.segment_decay + index * dim;
+        for (int u = 0; u < AHEAD; ++u) {
+            const int k = k0 + u;
+            const bool more = k + 1 < segments;
+            const size_t index = first + (size_t)k * stride;
+            local[u] = more ? a.segment_state[index * cells + cell] : 0.0f;
+            decay[u] = more ? a.segment_decay[index * a.dim + row] : 0.0f;
+        }
 #pragma unroll
-        for (int i = 0; i < R; ++i) {
-            if (row0 + i < dim) {
-                float* cell = place + (size_t)(row0 + i) * vdim + column;
-                const float local = k + 1 < segments ? *cell : 0.0f;
-                *cell = S[i];
-                if (k + 1 < segments) S[i] = fmaf(decay[row0 + i], S[i], local);
+        for (int u = 0; u < AHEAD; ++u) {
+            const int k = k0 + u;
+            if (k < segments) {
+                a.segment_state[(first + (size_t)k * stride) * cells + cell] = S;
+                if (k + 1 < segments) S = fmaf(decay[u], S, local[u]);
             }
         }
     }
@@ -272,7 +277,7 @@ LLM_EXPORT int llm_gla_recurrent(const void* proj, int row_width, int q_offset, 
             GLA_LAUNCH_MODE(R, GLA_ONE_PASS);                                                                           \
         } else {                                                                                                        \
             GLA_LAUNCH_MODE(R, GLA_LOCAL);                                                                              \
-            llm_launch(gla_scan_kernel<R>, dim3(n_seqs, heads), threads, 0, stream, a);                                 \
+            llm_launch(gla_scan_kernel, dim3(n_seqs, heads, (dim * vdim + 255) / 256), 256, 0, stream, a);                            \
             GLA_LAUNCH_MODE(R, GLA_OUTPUT);                                                                             \
         }                                                                                                               \
     } while (0)

@@ -248,6 +248,9 @@ def try_attention_precise(qkv, q_stride, batch, block_tables, k_pages, v_pages, 
 
 
 DIFF_KERNEL = os.environ.get("LLMSERVER_B200_DIFF_ATTENTION", "mma")      # "generic": always the kernel that takes every size
+# row tiles per block of the tiled kernel: 0 = by the step (2, and 2 key splits, with prompt portions; 1 and 4 key splits
+# for single tokens); 1, 2 or 4 force an arrangement
+DIFF_ROW_TILES = int(os.environ.get("LLMSERVER_B200_DIFF_ROW_TILES", "0"))
 
 
 def try_attention_diff(qkv, gate_column, batch, block_tables, k_pages, v_pages, n_q_heads, n_kv_heads, dim, value_dim, scale,
@@ -264,5 +267,5 @@ def try_attention_diff(qkv, gate_column, batch, block_tables, k_pages, v_pages, 
          block_tables.data_ptr(), block_tables.shape[-1], batch.q_start.data_ptr(), batch.context_len.data_ptr(), out.data_ptr(),
          batch.n_seqs, int(batch.max_q_len), n_q_heads, n_kv_heads, int(dim), int(value_dim), k_pages.shape[2], k_pages.shape[0],
          float(scale), float(cap or 0.0), int(window or 0), float(lam), float(eps), float(out_scale),
-         wait_error_flag(qkv.device).data_ptr(), stream_handle())
+         wait_error_flag(qkv.device).data_ptr(), DIFF_ROW_TILES, stream_handle())
     return True
