@@ -214,6 +214,35 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gate_up, T* __restrict_
     }
 }
 
+// The same, eight outputs per thread with 16-byte accesses (intermediate sizes that are a multiple of 8; the hardware
+// exponential and a fast division for 16-bit activations, whose rounding is far coarser than theirs).
+template <typename T>
+__global__ void clamped_glu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int intermediate, size_t chunks,
+                                       float limit, float alpha) {
+    pdl_trigger();
+    pdl_wait();
+    const int per_row = intermediate / 8;
+    for (size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x; c < chunks; c += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = c / per_row;
+        const int column = (int)(c % per_row) * 8;
+        const T* src = gate_up + row * 2 * (size_t)intermediate + column;
+        float gate[8], up[8], result[8];
+        load8<T>(src, gate);
+        load8<T>(src + intermediate, up);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (sizeof(T) == 2) {
+                const float g = fminf(gate[j], limit);
+                const float u = fminf(fmaxf(up[j], -limit), limit);
+                result[j] = __fdividef(g, 1.0f + __expf(-alpha * g)) * (u + 1.0f);
+            } else {
+                result[j] = gated_activation(gate[j], up[j], limit, alpha);
+            }
+        }
+        store8<T>(out + row * (size_t)intermediate + column, result);
+    }
+}
+
 LLM_EXPORT int llm_moe_route(const void* x, const float* router, const float* correction, int* chosen, float* weights,
                              int* counts, int n_tokens, int width, int experts, int top, float scale, int dtype,
                              cudaStream_t stream) {
@@ -312,6 +341,14 @@ LLM_EXPORT int llm_clamped_glu(const void* gate_up, void* out, int n_rows, int i
                                int dtype, cudaStream_t stream) {
     if (n_rows == 0 || intermediate == 0) return LLM_OK;
     const size_t total = (size_t)n_rows * intermediate;
+    if (intermediate % 8 == 0 && aligned16(gate_up) && aligned16(out)) {
+        const size_t chunks = total / 8;
+        size_t vec_blocks = (chunks + 255) / 256;
+        if (vec_blocks > 148 * 16) vec_blocks = 148 * 16;
+        LLM_DISPATCH_DTYPE(dtype, (llm_launch(clamped_glu_vec_kernel<T>, (unsigned)vec_blocks, 256, 0, stream, (const T*)gate_up,
+                                      (T*)out, intermediate, chunks, limit, alpha)));
+        return llm_check_launch("clamped_glu");
+    }
     size_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     LLM_DISPATCH_DTYPE(dtype, (llm_launch(clamped_glu_kernel<T>, (unsigned)blocks, 256, 0, stream, (const T*)gate_up, (T*)out,

@@ -31,10 +31,19 @@ __global__ void norm_rope_units_kernel(T* __restrict__ qkv, int row_width, const
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     float* values = unit_values + (size_t)warp * max_dim;
     const int position = positions[token];
+    const int half = rotary_dim >> 1;
+    // the token's cosines and sines, made once for all of its units
+    float2* rotation = reinterpret_cast<float2*>(unit_values + (size_t)warps * max_dim);
+    if (inv_freq) {
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float angle = (float)position * inv_freq[i];
+            rotation[i] = make_float2(cosf(angle), sinf(angle));
+        }
+        __syncthreads();
+    }
     const int q_units = n_q_heads * maps, k_units = n_kv_heads * maps;
     const int total_units = q_units + k_units + (value_dim > 0 ? n_kv_heads : 0);
     T* row = qkv + (size_t)token * row_width;
-    const int half = rotary_dim >> 1;
     for (int unit = blockIdx.y * warps + warp; unit < total_units; unit += gridDim.y * warps) {
         const bool is_q = unit < q_units;
         const bool is_k = !is_q && unit < q_units + k_units;
@@ -83,8 +92,7 @@ __global__ void norm_rope_units_kernel(T* __restrict__ qkv, int row_width, const
         __syncwarp();
         const int turning = (inv_freq && (is_q || is_k)) ? rotary_dim : 0;
         for (int i = lane; i < turning / 2; i += 32) {
-            const float angle = (float)position * inv_freq[i];
-            const float c = cosf(angle), s = sinf(angle);
+            const float c = rotation[i].x, s = rotation[i].y;
             const float u = values[i], v = values[half + i];
             Num<T>::store(dst + i, u * c - v * s);
             Num<T>::store(dst + half + i, v * c + u * s);
@@ -118,7 +126,7 @@ LLM_EXPORT int llm_norm_rope_units(void* qkv, int row_width, const float* bias, 
     int max_dim = q_dim > k_dim ? q_dim : k_dim;
     if (value_dim > max_dim) max_dim = value_dim;
     const int warps = 4;
-    const size_t shared = (size_t)warps * max_dim * sizeof(float);
+    const size_t shared = (size_t)warps * max_dim * sizeof(float) + (size_t)(rotary_dim / 2 + 1) * sizeof(float2);
     if (shared > 160 * 1024) {
         llm_set_error("norm_rope_units: units of %d elements need %zu bytes of shared memory", max_dim, shared);
         return LLM_REFUSED;
