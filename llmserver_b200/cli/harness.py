@@ -364,10 +364,10 @@ def _dikusun_mixers(width, heads, kv_heads):
     """Mixers of one width: differential attention whose two maps together are as wide as a dense head, a window of
     1024 tokens; latent attention with a latent of 128 (the widest head the tensor-core attention kernels take);
     gated linear attention with keys half and values as wide as the stream."""
-    return (dict(heads=heads, kv_heads=kv_heads, dim=64, vdim=128, scale=0.125, diff=0.3, softcap=50.0, mask={"size": 1024},
-                 rot={"base": 1000000.0, "dims": 64}),
+    return (dict(heads=heads, kv_heads=kv_heads, dim=64, vdim=128, scale=0.125, diff=0.2, softcap=30.0, mask={"size": 1024},
+                 rot={"base": 500000.0, "dims": 64}),
             dict(heads=16, dim=128, vdim=128, q_rank=width // 4, kv_rank=128, scale=128 ** -0.5),
-            dict(heads=width // 128, dim=64, vdim=128, tau=16.0, a_rank=16))
+            dict(heads=width // 128, dim=64, vdim=128, tau=8.0, a_rank=32))
 
 
 # Layer sizes that resemble served models, each as four layers of one kind of mixer and as a mix of the three; every

@@ -68,6 +68,8 @@ struct DiffParams {
     float scale, cap, lambda, eps, out_scale;
     int window, row_tiles;
     int* error_flag;
+    int block_splits;              // single tokens only: blocks that share a (sequence, key/value head) pair's keys
+    float* partials;               // [S, kv heads, block_splits * warp splits, 2 maps, group, DV + 2] when block_splits > 1
 };
 
 constexpr int kWarps = 8;
@@ -108,7 +110,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2) attention_diff_mma_kernel(Diff
     extern __shared__ uint4 diff_shared_raw[];
     unsigned char* shared = reinterpret_cast<unsigned char*>(diff_shared_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int sequence = blockIdx.y, kv_head = blockIdx.z;
+    const int sequence = blockIdx.y, kv_head = blockIdx.z % p.n_kv_heads, block_split = blockIdx.z / p.n_kv_heads;
     const int group = p.n_q_heads / p.n_kv_heads;
     const int begin = p.q_start[sequence], q_len = p.q_start[sequence + 1] - begin;
     const int context = p.context_len[sequence];
@@ -158,8 +160,9 @@ __global__ void __launch_bounds__(kWarps * 32, 2) attention_diff_mma_kernel(Diff
         const int key_high = warp_last;
         const int whole_low = p.window > 0 ? max(0, warp_last - p.window + 1) : 0, whole_high = warp_first;
         const int n_tiles = (key_high - key_low + KT) / KT;
-        const int per_split = (n_tiles + splits - 1) / splits;
-        const int tile_begin = split * per_split, tile_end = min(n_tiles, tile_begin + per_split);
+        const int all_splits = splits * p.block_splits;
+        const int per_split = (n_tiles + all_splits - 1) / all_splits;
+        const int tile_begin = (block_split * splits + split) * per_split, tile_end = min(n_tiles, tile_begin + per_split);
 
         for (int t = tile_begin; t < tile_end; ++t) {
             const int key0 = key_low + t * KT;
@@ -278,6 +281,22 @@ __global__ void __launch_bounds__(kWarps * 32, 2) attention_diff_mma_kernel(Diff
             }
         }
         __syncwarp();
+        if (p.block_splits > 1) {
+            // several blocks share the keys: the warp's rows go to global memory, and a kernel of its own merges them
+            const size_t slot = (((size_t)sequence * p.n_kv_heads + kv_head) * all_splits + block_split * splits + split) * 2 + map;
+            float* rows = p.partials + slot * group * (DV + 2);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int r = row0 + (lane >> 2) + 8 * h;
+                if (r < total_rows) {
+#pragma unroll
+                    for (int j = 0; j < DV / 8; ++j)
+                        *reinterpret_cast<float2*>(rows + (size_t)r * (DV + 2) + 8 * j + 2 * (lane & 3)) = make_float2(acc[j][2 * h], acc[j][2 * h + 1]);
+                    if ((lane & 3) == 0) *reinterpret_cast<float2*>(rows + (size_t)r * (DV + 2) + DV) = make_float2(running_max[h], running_sum[h]);
+                }
+            }
+            return;
+        }
         // the warp's partial result takes the place of its tiles: O [16 rows][DV], then max and sum [16][2]
         float* partial = reinterpret_cast<float*>(mine);
         float* statistics = partial + 16 * DV;
@@ -298,6 +317,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2) attention_diff_mma_kernel(Diff
             }
         }
     }
+    if (p.block_splits > 1) return;      // (uniform over the block)
     __syncthreads();
     // one warp per row: merge the splits of each map, subtract the maps, normalise the head, gate, store
     const int block_rows = min(16 * row_tiles, total_rows - block_row0);
@@ -347,6 +367,57 @@ __global__ void __launch_bounds__(kWarps * 32, 2) attention_diff_mma_kernel(Diff
     }
 }
 
+// Single tokens whose keys several blocks shared: one warp per (sequence, head) merges the partial results of all
+// splits for each map, subtracts the maps, normalises the head, applies the gate and stores.
+template <int DV>
+__global__ void attention_diff_merge_kernel(DiffParams p, int all_splits) {
+    pdl_trigger();
+    pdl_wait();
+    const int sequence = blockIdx.x, lane = threadIdx.x & 31;
+    const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (head >= p.n_q_heads) return;
+    const int group = p.n_q_heads / p.n_kv_heads;
+    const int kv_head = head / group, r = head % group;
+    const int token = p.q_start[sequence];
+    if (p.q_start[sequence + 1] - token != 1) return;      // this launch shape is for single tokens only
+    const float* base = p.partials + ((size_t)sequence * p.n_kv_heads + kv_head) * all_splits * 2 * group * (DV + 2);
+    float merged[2][DV / 32];
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        float top = -INFINITY;
+        for (int s = 0; s < all_splits; ++s) top = fmaxf(top, base[((size_t)(s * 2 + m) * group + r) * (DV + 2) + DV]);
+        float denominator = 0.0f;
+#pragma unroll
+        for (int i = 0; i < DV / 32; ++i) merged[m][i] = 0.0f;
+        for (int s = 0; s < all_splits; ++s) {
+            const float* row = base + ((size_t)(s * 2 + m) * group + r) * (DV + 2);
+            const float own_max = row[DV];
+            if (own_max == -INFINITY) continue;          // this split saw no key of the row
+            const float factor = __expf(own_max - top);
+            denominator += factor * row[DV + 1];
+#pragma unroll
+            for (int i = 0; i < DV / 32; ++i) merged[m][i] += factor * row[lane + 32 * i];
+        }
+        const float inverse = 1.0f / denominator;
+#pragma unroll
+        for (int i = 0; i < DV / 32; ++i) merged[m][i] *= inverse;
+    }
+    float sum_squares = 0.0f;
+#pragma unroll
+    for (int i = 0; i < DV / 32; ++i) {
+        merged[0][i] -= p.lambda * merged[1][i];
+        sum_squares += merged[0][i] * merged[0][i];
+    }
+    float factor = rsqrtf(warp_sum(sum_squares) / (float)DV + p.eps) * p.out_scale;
+    if (p.gate) {
+        const float g = __bfloat162float(p.gate[(size_t)token * p.gate_stride + head]);
+        factor *= 1.0f / (1.0f + __expf(-g));
+    }
+    __nv_bfloat16* dst = p.out + (size_t)token * p.n_q_heads * DV + (size_t)head * DV;
+#pragma unroll
+    for (int i = 0; i < DV / 32; ++i) dst[lane + 32 * i] = __float2bfloat16_rn(merged[0][i] * factor);
+}
+
 template <int DIM, int DV>
 int launch_diff(const DiffParams& p, int n_seqs, int max_q_len, cudaStream_t stream) {
     using Shape = DiffShape<DIM, DV>;
@@ -355,8 +426,12 @@ int launch_diff(const DiffParams& p, int n_seqs, int max_q_len, cudaStream_t str
     if (status != LLM_OK) return status;
     const int group = p.n_q_heads / p.n_kv_heads;
     const int rows = max_q_len * group;
-    dim3 grid((rows + 16 * p.row_tiles - 1) / (16 * p.row_tiles), n_seqs, p.n_kv_heads);
+    dim3 grid((rows + 16 * p.row_tiles - 1) / (16 * p.row_tiles), n_seqs, p.n_kv_heads * p.block_splits);
     llm_launch(attention_diff_mma_kernel<DIM, DV>, grid, kWarps * 32, shared, stream, p);
+    if (p.block_splits > 1) {
+        const int all_splits = p.block_splits * (kWarps / (2 * p.row_tiles));
+        llm_launch(attention_diff_merge_kernel<DV>, dim3(n_seqs, (p.n_q_heads + 3) / 4), 128, 0, stream, p, all_splits);
+    }
     return llm_check_launch("attention_diff_mma");
 }
 
@@ -370,7 +445,8 @@ LLM_EXPORT int llm_attention_diff_mma(const void* q, int q_stride, const void* g
                                       const void* v_pages, const int* block_tables, int max_blocks, const int* q_start,
                                       const int* context_len, void* out, int n_seqs, int max_q_len, int n_q_heads, int n_kv_heads,
                                       int dim, int value_dim, int page_size, int num_pages, float scale, float cap, int window,
-                                      float lambda, float eps, float out_scale, int* error_flag, int row_tiles, cudaStream_t stream) {
+                                      float lambda, float eps, float out_scale, int* error_flag, int row_tiles, int block_splits,
+                                      float* partials, cudaStream_t stream) {
     if (n_seqs == 0 || max_q_len == 0) return LLM_OK;
     if (!llm_attention_diff_mma_supports(dim, value_dim, n_q_heads, n_kv_heads) || page_size <= 0 || num_pages <= 0) {
         llm_set_error("attention_diff_mma: units of %d, values of %d, %d / %d heads are not supported", dim, value_dim, n_q_heads, n_kv_heads);
@@ -390,6 +466,9 @@ LLM_EXPORT int llm_attention_diff_mma(const void* q, int q_stride, const void* g
     // 2 row tiles (and 2 key splits) for steps with prompt portions, 1 (and 4 key splits) for steps of single tokens
     p.row_tiles = (row_tiles == 1 || row_tiles == 2 || row_tiles == 4) ? row_tiles : (max_q_len > 1 ? 2 : 1);
     p.error_flag = error_flag;
+    // several blocks per (sequence, key/value head) pair only for steps of single tokens whose group fits one row tile
+    p.block_splits = (max_q_len == 1 && p.row_tiles == 1 && n_q_heads / n_kv_heads <= 16 && partials && block_splits > 1) ? block_splits : 1;
+    p.partials = partials;
     if (dim == 64 && value_dim == 64) return launch_diff<64, 64>(p, n_seqs, max_q_len, stream);
     if (dim == 64 && value_dim == 128) return launch_diff<64, 128>(p, n_seqs, max_q_len, stream);
     if (dim == 128 && value_dim == 64) return launch_diff<128, 64>(p, n_seqs, max_q_len, stream);

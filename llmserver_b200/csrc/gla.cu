@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(R == 128 ? 256 : 512, R <= 16 ? 2 : 1) gla_rec
 
     for (int first = begin; first < end; first += GLA_TOKENS) {
         const int count = min(GLA_TOKENS, end - first);
-        __syncthreads();      // the last round's parts have been read
+        __syncthreads();      // the parts of the tokens before have been read
         for (int e = threadIdx.x; e < count * padded; e += blockDim.x) {
             const int t = e / padded, i = e % padded;
             float qv = 0.0f, kv = 0.0f, alpha = 0.0f;

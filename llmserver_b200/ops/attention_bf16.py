@@ -263,9 +263,27 @@ def try_attention_diff(qkv, gate_column, batch, block_tables, k_pages, v_pages, 
         return False
     check(qkv, "qkv", torch.bfloat16)
     gate = 0 if gate_column is None else qkv.data_ptr() + gate_column * qkv.element_size()
+    # A step of single tokens has few (sequence, key/value head) pairs: several blocks then share a pair's keys, four
+    # warp splits each, and leave partial results that a merge kernel adds up.  The count is a function of the batch's
+    # host-side shape (so a captured graph keeps it): about four key tiles of 16 per warp, at most 16 blocks a pair,
+    # and no more blocks than fill the GPU twice.
+    block_splits, partials, group = 1, None, n_q_heads // n_kv_heads
+    if batch.max_q_len == 1 and group <= 16 and DIFF_ROW_TILES in (0, 1):
+        span = min(int(window), batch.max_context) if window else batch.max_context
+        wanted = -(-span // (16 * 4 * 4))
+        room = max(1, 2 * _sm_count(qkv.device) // max(1, batch.n_seqs * n_kv_heads))
+        block_splits = max(1, min(wanted, room, 16))
+        if block_splits > 1:
+            key = ("attention_diff_partials", batch.n_seqs, n_kv_heads, block_splits, group, value_dim)
+            partials = batch.scratch.get(key)
+            if partials is None:
+                partials = torch.empty((batch.n_seqs, n_kv_heads, block_splits * 4, 2, group, value_dim + 2), dtype=torch.float32,
+                                       device=qkv.device)
+                batch.scratch[key] = partials
     call("llm_attention_diff_mma", qkv.data_ptr(), row_width, gate, row_width, k_pages.data_ptr(), v_pages.data_ptr(),
          block_tables.data_ptr(), block_tables.shape[-1], batch.q_start.data_ptr(), batch.context_len.data_ptr(), out.data_ptr(),
          batch.n_seqs, int(batch.max_q_len), n_q_heads, n_kv_heads, int(dim), int(value_dim), k_pages.shape[2], k_pages.shape[0],
          float(scale), float(cap or 0.0), int(window or 0), float(lam), float(eps), float(out_scale),
-         wait_error_flag(qkv.device).data_ptr(), DIFF_ROW_TILES, stream_handle())
+         wait_error_flag(qkv.device).data_ptr(), DIFF_ROW_TILES, block_splits, 0 if partials is None else partials.data_ptr(),
+         stream_handle())
     return True

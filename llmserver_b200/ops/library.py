@@ -29,7 +29,7 @@ SIGNATURES = {
     "llm_norm_rope_units": [_P, _I, _P, _P, _P, _F, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _I, _S],
     "llm_attention_diff": [_P, _I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _F, _F, _F, _P, _I, _S],
     "llm_attention_diff_mma_supports": [_I, _I, _I, _I],
-    "llm_attention_diff_mma": [_P, _I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _F, _F, _F, _P, _I, _S],
+    "llm_attention_diff_mma": [_P, _I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _F, _F, _F, _P, _I, _I, _P, _S],
     "llm_gla_supports": [_I, _I],
     "llm_gla_recurrent": [_P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _F, _F, _I, _I, _I, _I, _P, _P, _S],
     "llm_moe_route": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _S],

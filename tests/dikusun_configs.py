@@ -70,9 +70,9 @@ TENSOR_CORE_SIZES = {
     "layers": [
         {"type": "latent_attention", "mixer": _latent(4, 32, 64, 64, 128, 0.18), "mlp": _dense(256, 2.0)},
         {"type": "attention", "mixer": _attention(4, 2, 64, 64, 0.125, 0.3, 70, 32, base=1e5, softcap=40.0), "mlp": None},
-        {"type": "gla", "mixer": _gla(2, 64, 128, 16.0, 16), "mlp": _dense(128, 1.5)},
+        {"type": "gla", "mixer": _gla(2, 64, 128, 12.0, 16), "mlp": _dense(128, 2.5)},
         {"type": "latent_attention", "mixer": _latent(8, 64, 32, 128, 64, 0.125), "mlp": None},
-        {"type": "attention", "mixer": _attention(2, 1, 128, 128, 0.09, 0.1, 150, 128, base=1e4), "mlp": _dense(128, 1.5)},
+        {"type": "attention", "mixer": _attention(2, 1, 128, 128, 0.09, 0.1, 150, 128, base=1e4), "mlp": _dense(128, 0.9)},
     ],
 }
 
