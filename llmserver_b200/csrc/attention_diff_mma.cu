@@ -384,21 +384,30 @@ __global__ void attention_diff_merge_kernel(DiffParams p, int all_splits) {
     float merged[2][DV / 32];
 #pragma unroll
     for (int m = 0; m < 2; ++m) {
-        float top = -INFINITY;
-        for (int s = 0; s < all_splits; ++s) top = fmaxf(top, base[((size_t)(s * 2 + m) * group + r) * (DV + 2) + DV]);
-        float denominator = 0.0f;
+        // lanes own the splits' maxima and sums (at most 64 splits), so these loads do not wait for one another
+        float own_max[2], own_sum[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int s = lane + 32 * u;
+            float2 statistics = make_float2(-INFINITY, 0.0f);
+            if (s < all_splits) statistics = *reinterpret_cast<const float2*>(base + ((size_t)(s * 2 + m) * group + r) * (DV + 2) + DV);
+            own_max[u] = statistics.x;
+            own_sum[u] = statistics.y;
+        }
+        const float top = warp_max(fmaxf(own_max[0], own_max[1]));
+        float factor[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) factor[u] = own_max[u] == -INFINITY ? 0.0f : __expf(own_max[u] - top);      // a split that saw no key
+        const float inverse = 1.0f / warp_sum(factor[0] * own_sum[0] + factor[1] * own_sum[1]);
 #pragma unroll
         for (int i = 0; i < DV / 32; ++i) merged[m][i] = 0.0f;
+#pragma unroll 4
         for (int s = 0; s < all_splits; ++s) {
+            const float f = __shfl_sync(0xffffffffu, s < 32 ? factor[0] : factor[1], s & 31);
             const float* row = base + ((size_t)(s * 2 + m) * group + r) * (DV + 2);
-            const float own_max = row[DV];
-            if (own_max == -INFINITY) continue;          // this split saw no key of the row
-            const float factor = __expf(own_max - top);
-            denominator += factor * row[DV + 1];
 #pragma unroll
-            for (int i = 0; i < DV / 32; ++i) merged[m][i] += factor * row[lane + 32 * i];
+            for (int i = 0; i < DV / 32; ++i) merged[m][i] = fmaf(f, row[lane + 32 * i], merged[m][i]);
         }
-        const float inverse = 1.0f / denominator;
 #pragma unroll
         for (int i = 0; i < DV / 32; ++i) merged[m][i] *= inverse;
     }

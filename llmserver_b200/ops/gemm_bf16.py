@@ -122,7 +122,8 @@ _CLOSE_SPLITS = float(os.environ.get("LLMSERVER_B200_GEMM_CLOSE_SPLITS", "0.04")
 def _fastest_split(timed: list) -> int:
     """``timed``: (split, milliseconds) of this package's kernel; the largest split among the (nearly) fastest."""
     fastest = min(elapsed for _, elapsed in timed)
-    return max(split for split, elapsed in timed if elapsed <= fastest * (1.0 + _CLOSE_SPLITS))
+    # (a profiler that serialises launches can report times of zero or below: the margin must not turn negative)
+    return max(split for split, elapsed in timed if elapsed <= fastest + abs(fastest) * _CLOSE_SPLITS)
 
 
 def _time_in_step(run, device, repeats: int = 10) -> float:
