@@ -48,8 +48,11 @@ struct GlaArgs {
 // MODE 0: a sequence's tokens in one pass, from and into its state slot.  1: pass A of the segmented form.  3: pass C.
 enum : int { GLA_ONE_PASS = 0, GLA_LOCAL = 1, GLA_OUTPUT = 3 };
 
-template <typename T, typename W, int R, int MODE>
-__global__ void __launch_bounds__(R == 128 ? 256 : 512, R <= 16 ? 2 : 1) gla_recurrent_kernel(GlaArgs a) {
+// R = 128 comes with 256 threads, where a thread's 128 rows of state fit its registers, and, for sizes nothing else
+// takes, with 512 (R given as 129), where they spill: slow, but every size up to 256 x 256 then runs.
+template <typename T, typename W, int RR, int MODE>
+__global__ void __launch_bounds__(RR == 128 ? 256 : 512, RR <= 16 ? 2 : 1) gla_recurrent_kernel(GlaArgs a) {
+    constexpr int R = RR == 129 ? 128 : RR;
     pdl_trigger();
     pdl_wait();
     extern __shared__ float4 gla_shared_raw[];
@@ -227,6 +230,7 @@ static int gla_rows_per_thread(int dim, int column_threads) {
         // 128 rows of state per thread leave room for 256 threads' registers only
         if (partitions * column_threads <= (choices[c] == 128 ? 256 : 512)) return choices[c];
     }
+    if ((dim + 127) / 128 * column_threads <= 512) return 129;      // 128 rows with 512 threads: the state spills
     return 0;
 }
 
@@ -250,7 +254,8 @@ LLM_EXPORT int llm_gla_recurrent(const void* proj, int row_width, int q_offset, 
     a.z = z; a.z_bias = z_bias; a.weight = weight; a.state = state; a.state_slots = state_slots; a.q_start = q_start; a.out = out;
     a.heads = heads; a.dim = dim; a.vdim = vdim;
     a.column_threads = (vdim + 31) / 32 * 32;
-    const int rows = gla_rows_per_thread(dim, a.column_threads);
+    const int choice = gla_rows_per_thread(dim, a.column_threads);
+    const int rows = choice == 129 ? 128 : choice;
     a.partitions = (dim + rows - 1) / rows;
     a.padded_dim = a.partitions * rows;
     a.inverse_tau = inverse_tau; a.q_scale = q_scale; a.eps = eps;
@@ -282,10 +287,11 @@ LLM_EXPORT int llm_gla_recurrent(const void* proj, int row_width, int q_offset, 
         }                                                                                                               \
     } while (0)
     LLM_DISPATCH_DTYPE_WEIGHT(dtype, weight_dtype, {
-        if (rows == 16) GLA_LAUNCH(16);
-        else if (rows == 32) GLA_LAUNCH(32);
-        else if (rows == 64) GLA_LAUNCH(64);
-        else GLA_LAUNCH(128);
+        if (choice == 16) GLA_LAUNCH(16);
+        else if (choice == 32) GLA_LAUNCH(32);
+        else if (choice == 64) GLA_LAUNCH(64);
+        else if (choice == 128) GLA_LAUNCH(128);
+        else GLA_LAUNCH(129);
     });
 #undef GLA_LAUNCH
 #undef GLA_LAUNCH_MODE

@@ -380,7 +380,7 @@ def test_per_head_products(dtype, heads, rows, inner, tokens):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,dim,vdim,tau", [(2, 24, 40, 8.0), (5, 8, 16, 1.0), (1, 72, 33, 32.0), (2, 64, 128, 16.0), (3, 128, 64, 4.0),
-                                                (1, 200, 96, 16.0), (2, 16, 256, 2.0)])
+                                                (1, 200, 96, 16.0), (2, 16, 256, 2.0), (1, 256, 256, 8.0), (2, 200, 160, 3.0)])
 def test_gated_linear_attention_kernel(dtype, heads, dim, vdim, tau):
     """Three sequences in one step: one continues from a state that an earlier step left (in another slot order), one
     starts from zero, one is a single token.  Decays run from 'forgets at once' to 'keeps for hundreds of tokens'; the
